@@ -72,7 +72,13 @@ class AttentionSpec:
     when it equals ``head_dim``.  ``bias``: the q, k and v projections add a bias.
     ``qk_norm_eps``: not None puts an RMS norm over each query and key head (one weight of
     ``head_dim`` for the queries and one for the keys, shared by the heads) before the
-    position encoding.
+    position encoding.  ``conv_taps`` > 1 puts a causal convolution over time on every
+    channel of q and k (``conv_taps`` weights a channel, the last one on the token itself, no
+    bias) directly after the projection; the last ``conv_taps - 1`` projected rows of a
+    sequence are per-request state.  ``value_from_key``: there is no value projection, a key
+    head as it leaves the convolution (before its norm) is the value.  ``head_gate``: the
+    output of head h is multiplied by ``sigmoid(W_g x)_h``, one number a head, before the
+    output product.
     """
 
     kind: str = "attention"
@@ -88,6 +94,9 @@ class AttentionSpec:
     v_head_dim: Optional[int] = None
     bias: bool = False
     qk_norm_eps: Optional[float] = None
+    conv_taps: int = 0
+    value_from_key: bool = False
+    head_gate: bool = False
 
     @property
     def value_dim(self) -> int:
@@ -97,12 +106,14 @@ class AttentionSpec:
     def plain(self) -> bool:
         """Whether this is the attention that the kernels of the dense decoder take."""
         return (not self.keep_first and self.v_head_dim in (None, self.head_dim)
-                and not self.bias and self.qk_norm_eps is None)
+                and not self.bias and self.qk_norm_eps is None and self.conv_taps == 0
+                and not self.value_from_key and not self.head_gate)
 
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
-    """``down(act(gate(x)) * up(x))`` with a fused ``[gate; up]`` matrix."""
+    """``down(act(gate(x)) * up(x))`` with a fused ``[gate; up]`` matrix; ``activation``:
+    "silu" or "gelu_tanh"."""
 
     kind: str = "gated_mlp"
     hidden_size: int = 0
@@ -189,7 +200,11 @@ class LatentAttentionSpec:
     ``(q_plain . W_uk[h] c + q_rot . k_rot) * scale`` and reads the value ``W_uv[h] c``.
     ``position`` rotates the ``rot_dim`` part of queries and of the shared key.
     ``window``: None keeps every key; W lets position p see p-W+1 .. p.  ``gated``:
-    the concatenated heads are multiplied by sigmoid(W_g x) before the output product.
+    the concatenated heads are multiplied by sigmoid(W_g x) before the output product,
+    feature by feature, or, with ``gate_per_head``, by one number a head (W_g then has
+    ``num_heads`` rows).  ``q_rank``: not None sends the queries through a latent of that
+    size, ``q = W_uq norm(W_dq x)`` (RMS norm with a plain weight).  ``shares_kv``: the
+    layer has no down-projection and reads the rows that an earlier layer cached.
     """
 
     kind: str = "latent_attention"
@@ -205,6 +220,8 @@ class LatentAttentionSpec:
     norm_eps: float = 1e-6
     gated: bool = True
     shares_kv: bool = False
+    gate_per_head: bool = False
+    q_rank: Optional[int] = None
 
 
 @dataclass(frozen=True)

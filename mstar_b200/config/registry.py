@@ -98,3 +98,8 @@ def _register_builtin() -> None:
 
     if "Vudivik" not in _ARCHITECTURES:
         register_architecture("Vudivik", VudivikConfig, vudivik_checkpoint_map)
+    from ..weights.relurax import relurax_checkpoint_map
+    from .relurax import ReluraxConfig
+
+    if "Relurax" not in _ARCHITECTURES:
+        register_architecture("Relurax", ReluraxConfig, relurax_checkpoint_map)

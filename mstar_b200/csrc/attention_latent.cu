@@ -18,7 +18,8 @@
 //
 // The first kernel fills the cache: it normalises the latent part of the down-projection
 // (RMS, plain weight), rotates the shared key part and the rotated part of every query head
-// (pairs (2i, 2i+1), angle = position * freq_i in double precision), and writes the row.
+// (pairs (2i, 2i+1) or (i, i + dims/2), angle = position * freq_i in double precision), and
+// writes the row; it also norms a query latent where the queries go through one.
 #include "common.cuh"
 #include "mma_util.cuh"
 
@@ -737,8 +738,10 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
 // ---------------------------------------------------------------- cache fill + rotation
 struct LatentFillArgs {
     int heads, qk_dim, rot, rot_dims, rank, page_size, bt_stride;
-    int ld;        // elements between tokens of the fused product
-    int dkv_off;   // column of the first down-projected feature
+    int ldq;        // elements between tokens of the queries
+    int ld_dkv;     // elements between tokens of the down-projection
+    int interleaved;        // 1: pairs (2i, 2i+1); 0: pairs (i, i + rot_dims/2)
+    int q_rank, ld_qlat, ld_qlat_out;   // the query latent: features, strides in and out
     float eps;
 };
 
@@ -751,64 +754,108 @@ __device__ __forceinline__ void rotate_pair(float u, float v, int position, doub
     y = v * c + u * s;
 }
 
-template <typename A>
-__global__ void latent_fill_kernel(A* __restrict__ proj, const float* __restrict__ norm_w,
+// One block per token; three jobs, each left out when its pointer is null:
+//   dkv   [rank latent | rot key] features of the down-projection (type D): the latent is
+//         RMS-normed (plain weight), the first rot_dims key features are rotated, and the row
+//         goes into the token's cache slot;
+//   q     the queries, head by head [qk_dim plain | rot rotated]: the first rot_dims features
+//         of every head's rotated part are rotated in place;
+//   qlat  q_rank features of a query latent (type D): RMS-normed with a plain weight into
+//         qlat_out (type A), the rows the query up-projection reads.
+template <typename A, typename D>
+__global__ void latent_fill_kernel(A* q, const D* dkv, const float* __restrict__ norm_w,
                                    const double* __restrict__ freq, const int* __restrict__ positions,
                                    const int* __restrict__ cache_pos, const int* __restrict__ token_req,
                                    const int* __restrict__ block_table, A* __restrict__ cache,
+                                   const D* qlat, const float* __restrict__ qlat_w, A* qlat_out,
                                    LatentFillArgs a) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, tid = threadIdx.x;
-    proj = pdl_after(proj, pdl_wait());
-    A* row = proj + (size_t)t * a.ld;
-    const A* dkv = row + a.dkv_off;
-    const int pos = positions[t], cp = cache_pos[t];
-    const int page = block_table[(size_t)token_req[t] * a.bt_stride + cp / a.page_size];
-    A* dst = cache + ((size_t)page * a.page_size + cp % a.page_size) * (a.rank + a.rot);
-
-    float ss = 0.f;
-    for (int i = tid; i < a.rank; i += blockDim.x) {
-        const float v = to_float(dkv[i]);
-        ss = fmaf(v, v, ss);
-    }
-    const float inv = rsqrtf(block_sum(ss, scratch) / (float)a.rank + a.eps);
-    for (int i = tid; i < a.rank; i += blockDim.x)
-        dst[i] = from_float<A>(to_float(dkv[i]) * inv * norm_w[i]);
-    // the shared key part: rotated pairs, then what lies beyond the rotated dimensions
+    const unsigned long long waited = pdl_wait();
+    const int pos = positions[t];
     const int half = a.rot_dims / 2;
-    for (int i = tid; i < half; i += blockDim.x) {
-        float x, y;
-        rotate_pair(to_float(dkv[a.rank + 2 * i]), to_float(dkv[a.rank + 2 * i + 1]), pos, freq[i], x, y);
-        dst[a.rank + 2 * i] = from_float<A>(x);
-        dst[a.rank + 2 * i + 1] = from_float<A>(y);
+    const int second = a.interleaved ? 1 : half;          // distance between a pair's features
+    const int step = a.interleaved ? 2 : 1;               // distance between two pairs
+    if (dkv != nullptr) {
+        const D* row = pdl_after(dkv, waited) + (size_t)t * a.ld_dkv;
+        const int cp = cache_pos[t];
+        const int page = block_table[(size_t)token_req[t] * a.bt_stride + cp / a.page_size];
+        A* dst = cache + ((size_t)page * a.page_size + cp % a.page_size) * (a.rank + a.rot);
+        float ss = 0.f;
+        for (int i = tid; i < a.rank; i += blockDim.x) {
+            const float v = to_float(row[i]);
+            ss = fmaf(v, v, ss);
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)a.rank + a.eps);
+        for (int i = tid; i < a.rank; i += blockDim.x)
+            dst[i] = from_float<A>(to_float(row[i]) * inv * norm_w[i]);
+        // the shared key part: rotated pairs, then what lies beyond the rotated dimensions
+        for (int i = tid; i < half; i += blockDim.x) {
+            float x, y;
+            rotate_pair(to_float(row[a.rank + step * i]), to_float(row[a.rank + step * i + second]),
+                        pos, freq[i], x, y);
+            dst[a.rank + step * i] = from_float<A>(x);
+            dst[a.rank + step * i + second] = from_float<A>(y);
+        }
+        for (int i = a.rot_dims + tid; i < a.rot; i += blockDim.x)
+            dst[a.rank + i] = from_float<A>(to_float(row[a.rank + i]));
     }
-    for (int i = a.rot_dims + tid; i < a.rot; i += blockDim.x) dst[a.rank + i] = dkv[a.rank + i];
-    // the rotated part of every query head, in place
-    for (int idx = tid; idx < a.heads * half; idx += blockDim.x) {
-        const int h = idx / half, i = idx - h * half;
-        A* q = row + (size_t)h * (a.qk_dim + a.rot) + a.qk_dim;
-        float x, y;
-        rotate_pair(to_float(q[2 * i]), to_float(q[2 * i + 1]), pos, freq[i], x, y);
-        q[2 * i] = from_float<A>(x);
-        q[2 * i + 1] = from_float<A>(y);
+    if (q != nullptr) {
+        A* row = pdl_after(q, waited) + (size_t)t * a.ldq;
+        for (int idx = tid; idx < a.heads * half; idx += blockDim.x) {
+            const int h = idx / half, i = idx - h * half;
+            A* qh = row + (size_t)h * (a.qk_dim + a.rot) + a.qk_dim;
+            float x, y;
+            rotate_pair(to_float(qh[step * i]), to_float(qh[step * i + second]), pos, freq[i], x, y);
+            qh[step * i] = from_float<A>(x);
+            qh[step * i + second] = from_float<A>(y);
+        }
+    }
+    if (qlat != nullptr) {
+        const D* row = pdl_after(qlat, waited) + (size_t)t * a.ld_qlat;
+        float ss = 0.f;
+        for (int i = tid; i < a.q_rank; i += blockDim.x) {
+            const float v = to_float(row[i]);
+            ss = fmaf(v, v, ss);
+        }
+        const float inv = rsqrtf(block_sum(ss, scratch) / (float)a.q_rank + a.eps);
+        A* dst = qlat_out + (size_t)t * a.ld_qlat_out;
+        for (int i = tid; i < a.q_rank; i += blockDim.x)
+            dst[i] = from_float<A>(to_float(row[i]) * inv * qlat_w[i]);
     }
 }
 
-MSTAR_API int mstar_latent_fill(void* proj, int act_dtype, int ld, int dkv_off, const float* norm_w,
-                                const double* freq, const int* positions, const int* cache_pos,
-                                const int* token_req, const int* block_table, int bt_stride,
-                                void* cache, int num_tokens, int heads, int qk_dim, int rot,
-                                int rot_dims, int rank, int page_size, float eps, void* stream) {
+// `in_dtype`: the type of dkv and qlat (float, or the activation type).  Returns -1 for a
+// rotation over an odd number of features or more than there are, and for float activations
+// with inputs that are not float.
+MSTAR_API int mstar_latent_fill(void* q, int ldq, const void* dkv, int ld_dkv, int in_dtype,
+                                int act_dtype, const float* norm_w, const double* freq,
+                                const int* positions, const int* cache_pos, const int* token_req,
+                                const int* block_table, int bt_stride, void* cache,
+                                const void* qlat, int ld_qlat, const float* qlat_w, void* qlat_out,
+                                int ld_qlat_out, int q_rank, int num_tokens, int heads, int qk_dim,
+                                int rot, int rot_dims, int rank, int page_size, int interleaved,
+                                float eps, void* stream) {
     if (num_tokens <= 0) return 0;
-    if (rot_dims % 2 != 0 || rot_dims > rot) return -1;
+    if (rot_dims % 2 != 0 || rot_dims > rot || rot_dims < 0) return -1;
+    if (act_dtype == MSTAR_F32 && in_dtype != MSTAR_F32) return -1;
+    if (dkv != nullptr && (!norm_w || !cache || !block_table)) return -1;
+    if (qlat != nullptr && (!qlat_w || !qlat_out || q_rank <= 0)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
-    LatentFillArgs a{heads, qk_dim, rot, rot_dims, rank, page_size, bt_stride, ld, dkv_off, eps};
+    LatentFillArgs a{heads, qk_dim, rot, rot_dims, rank, page_size, bt_stride, ldq, ld_dkv,
+                     interleaved, q_rank, ld_qlat, ld_qlat_out, eps};
     const int threads = rank >= 512 ? 256 : 128;
-    if (act_dtype == MSTAR_F32)
-        mstar_launch((latent_fill_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, (float*)proj,
-                     norm_w, freq, positions, cache_pos, token_req, block_table, (float*)cache, a);
-    else
-        mstar_launch((latent_fill_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, (bf16*)proj,
-                     norm_w, freq, positions, cache_pos, token_req, block_table, (bf16*)cache, a);
+#define GO(A, D)                                                                                   \
+    mstar_launch((latent_fill_kernel<A, D>), dim3(num_tokens), dim3(threads), 0, s, (A*)q,         \
+                 (const D*)dkv, norm_w, freq, positions, cache_pos, token_req, block_table,        \
+                 (A*)cache, (const D*)qlat, qlat_w, (A*)qlat_out, a)
+    if (act_dtype == MSTAR_F32) {
+        GO(float, float);
+    } else if (in_dtype == MSTAR_F32) {
+        GO(bf16, float);
+    } else {
+        GO(bf16, bf16);
+    }
+#undef GO
     return launch_status();
 }

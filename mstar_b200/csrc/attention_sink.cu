@@ -2,6 +2,11 @@
 // value size of its own, biased projections and an RMS norm per query and key head.
 //
 //   prepare   row = [q: nq*hd | k: nkv*hd | v: nkv*vd] (float, the fused projection) + bias;
+//             with `taps` > 0 every q and k channel first passes a causal convolution over
+//             time, y_t = sum_j w[c][j] u_(t - taps + 1 + j), the rows before a portion's
+//             start taken from the request's state slot (advance moves that state on);
+//             with `v_from_k` the row has no v part and a key head as it stands here, before
+//             its norm, is written as the value head;
 //             every q and k head is divided by its root mean square (eps inside the root)
 //             and scaled by a weight shared by the heads; the first `rot` features of q and
 //             k are rotated (feature i with i + rot/2, angle position * freq[i]); q goes to
@@ -20,7 +25,29 @@ struct PrepArgs {
     int nq, nkv, hd, vd, rot, page_size, bt_stride, q_stride_out;
     float eps;
     int norm;       // 1: q and k heads are normed
+    int row_stride; // floats between the rows of two tokens
+    int taps;       // 0: no convolution
+    int v_from_k;   // 1: the values are the key heads before their norm
+    long long state_stride;     // floats between the state of two slots
 };
+
+// The convolved value of channel `col` (a column of q or k) of token t, the i-th of its
+// portion: taps - 1 earlier rows come from the portion itself or, before its start, from
+// the slot, which holds the request's last taps - 1 rows of [q | k] channels in time order.
+template <typename W>
+__device__ __forceinline__ float conv_feature(const float* __restrict__ row, const W* __restrict__ w,
+                                              const float* __restrict__ state, int col, int chan,
+                                              int channels, int i, const PrepArgs& a) {
+    float y = 0.f;
+    const int keep = a.taps - 1;
+    for (int j = 0; j < a.taps; ++j) {
+        const int back = keep - j;                       // rows before this token
+        const float u = back <= i ? *(row - (ptrdiff_t)back * a.row_stride + col)
+                                  : state[(size_t)(keep + i - back) * channels + col];
+        y = fmaf(to_float(w[(size_t)chan * a.taps + j]), u, y);
+    }
+    return y;
+}
 
 // One block per token.  Sines and cosines of the token's angles are made once (double
 // precision product) and shared by all heads.
@@ -31,7 +58,9 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
                     const double* __restrict__ freq, const int* __restrict__ positions,
                     const int* __restrict__ cache_pos, const int* __restrict__ token_req,
                     const int* __restrict__ block_table, A* __restrict__ q_out,
-                    A* __restrict__ kv_cache, PrepArgs a) {
+                    A* __restrict__ kv_cache, const W* __restrict__ conv_q,
+                    const W* __restrict__ conv_k, const int* __restrict__ qo_indptr,
+                    const int* __restrict__ slots, const float* state, PrepArgs a) {
     extern __shared__ float sm[];
     const int half = a.rot / 2;
     float* cs = sm;                            // [half] cosines, [half] sines
@@ -52,15 +81,23 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
         cs[half + i] = s;
     }
     __syncthreads();
-    const int row_len = (a.nq + a.nkv) * a.hd + a.nkv * a.vd;
-    const float* row = qkv + (size_t)t * row_len;
+    const float* row = qkv + (size_t)t * a.row_stride;
+    const int channels = (a.nq + a.nkv) * a.hd;          // what the convolution runs over
+    int local = 0;                                       // the token's place in its portion
+    const float* slot_state = nullptr;
+    if (a.taps > 0) {
+        const int e = token_req[t];
+        local = t - qo_indptr[e];
+        slot_state = pdl_after(state, waited) + (size_t)slots[e] * a.state_stride;
+    }
     const int key = cache_pos[t];
     const int page = block_table[(size_t)token_req[t] * a.bt_stride + key / a.page_size];
     const int slot = key % a.page_size;
     const size_t page_elems = (size_t)a.nkv * a.page_size * (a.hd + a.vd);
     A* page_base = kv_cache + (size_t)page * page_elems;
     float* mine = heads + warp * a.hd;
-    for (int h = warp; h < a.nq + 2 * a.nkv; h += nwarps) {
+    const int nheads = a.v_from_k ? a.nq + a.nkv : a.nq + 2 * a.nkv;
+    for (int h = warp; h < nheads; h += nwarps) {
         if (h >= a.nq + a.nkv) {               // a value head: bias, then the page
             const int g = h - a.nq - a.nkv;
             const int off = (a.nq + a.nkv) * a.hd + g * a.vd;
@@ -76,9 +113,21 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
         const bool is_q = h < a.nq;
         const int off = h * a.hd;
         float ss = 0.f;
+        A* as_value = (!is_q && a.v_from_k)
+                          ? page_base + (size_t)a.nkv * a.page_size * a.hd +
+                                ((size_t)(h - a.nq) * a.page_size + slot) * a.vd
+                          : nullptr;
         for (int d = lane; d < a.hd; d += 32) {
-            float v = row[off + d];
-            if (bias != nullptr) v += to_float(bias[off + d]);
+            float v;
+            if (a.taps > 0) {
+                v = is_q ? conv_feature(row, conv_q, slot_state, off + d, off + d, channels, local, a)
+                         : conv_feature(row, conv_k, slot_state, off + d, off + d - a.nq * a.hd,
+                                        channels, local, a);
+            } else {
+                v = row[off + d];
+                if (bias != nullptr) v += to_float(bias[off + d]);
+            }
+            if (as_value != nullptr) as_value[d] = from_float<A>(v);
             mine[d] = v;
             ss = fmaf(v, v, ss);
         }
@@ -110,24 +159,69 @@ MSTAR_API int mstar_sink_prepare(const float* qkv, const void* bias, const void*
                                  const int* positions, const int* cache_pos, const int* token_req,
                                  const int* block_table, int bt_stride, void* q_out,
                                  void* kv_cache, int act_dtype, int tokens, int nq, int nkv, int hd,
-                                 int vd, int rot, int page_size, float eps, int norm, void* stream) {
+                                 int vd, int rot, int page_size, float eps, int norm,
+                                 int row_stride, const void* conv_q, const void* conv_k, int taps,
+                                 int v_from_k, const int* qo_indptr, const int* slots,
+                                 const float* state, long long state_stride, void* stream) {
     if (tokens <= 0) return 0;
     if (hd <= 0 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0) return -1;
+    if (taps < 0 || (v_from_k && vd != hd)) return -1;
+    if (taps > 0 && (bias != nullptr || !conv_q || !conv_k || !qo_indptr)) return -1;
+    if (taps > 1 && (!slots || !state)) return -1;
+    if (row_stride < (nq + nkv) * hd + (v_from_k ? 0 : nkv * vd)) return -1;
     const int threads = 256;
     const size_t smem = sizeof(float) * ((size_t)rot + (size_t)(threads / 32) * hd);
     if (smem > 48 * 1024) return -1;
-    PrepArgs a{nq, nkv, hd, vd, rot, page_size, bt_stride, nq * hd, eps, norm};
+    PrepArgs a{nq, nkv, hd, vd, rot, page_size, bt_stride, nq * hd, eps, norm, row_stride, taps,
+               v_from_k, state_stride};
     cudaStream_t s = (cudaStream_t)stream;
 #define GO(A, W)                                                                                  \
     mstar_launch((sink_prepare_kernel<A, W>), dim3(tokens), dim3(threads), smem, s, qkv,          \
                  (const W*)bias, (const W*)q_norm, (const W*)k_norm, freq, positions, cache_pos,  \
-                 token_req, block_table, (A*)q_out, (A*)kv_cache, a)
+                 token_req, block_table, (A*)q_out, (A*)kv_cache, (const W*)conv_q,               \
+                 (const W*)conv_k, qo_indptr, slots, state, a)
     if (act_dtype == MSTAR_F32) {
         if (weight_dtype == MSTAR_F32) { GO(float, float); } else { GO(float, bf16); }
     } else {
         if (weight_dtype == MSTAR_F32) { GO(bf16, float); } else { GO(bf16, bf16); }
     }
 #undef GO
+    return launch_status();
+}
+
+// ------------------------------------------------------------------ advance
+// After prepare: the slot of every entry keeps the last taps - 1 rows of its sequence's
+// projected [q | k] channels (before the convolution).  A portion shorter than that keeps the
+// newer part of what the slot held.  A thread per entry and channel, oldest row first: row s
+// is read from s + n, which is written later or not at all.
+__global__ void conv_state_advance_kernel(const float* __restrict__ qkv, int row_stride, int channels,
+                                          int taps, const int* __restrict__ qo_indptr,
+                                          const int* __restrict__ slots, float* state,
+                                          long long state_stride) {
+    const unsigned long long waited = pdl_wait();
+    qkv = pdl_after(qkv, waited);
+    state = pdl_after(state, waited);
+    const int e = blockIdx.y;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int start = qo_indptr[e], n = qo_indptr[e + 1] - start, keep = taps - 1;
+    float* st = state + (size_t)slots[e] * state_stride;
+    for (int s = 0; s < keep; ++s) {
+        const int src = n - keep + s;                    // place in the portion, or before it
+        st[(size_t)s * channels + c] = src >= 0 ? qkv[(size_t)(start + src) * row_stride + c]
+                                                : st[(size_t)(s + n) * channels + c];
+    }
+}
+
+MSTAR_API int mstar_conv_state_advance(const float* qkv, int row_stride, int channels, int taps,
+                                       const int* qo_indptr, const int* slots, float* state,
+                                       long long state_stride, int entries, void* stream) {
+    if (entries <= 0 || taps <= 1 || channels <= 0) return 0;
+    if (!qkv || !qo_indptr || !slots || !state) return -1;
+    const int threads = 128;
+    mstar_launch(conv_state_advance_kernel, dim3((channels + threads - 1) / threads, entries),
+                 dim3(threads), 0, (cudaStream_t)stream, qkv, row_stride, channels, taps, qo_indptr,
+                 slots, state, state_stride);
     return launch_status();
 }
 

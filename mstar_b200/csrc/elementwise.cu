@@ -241,12 +241,24 @@ MSTAR_API int mstar_gather_add_rows(const float* resid, const void* delta, int a
     return launch_status();
 }
 
-// ------------------------------------------------------------ SiLU(gate)*up
+// ------------------------------------------------------------ act(gate)*up
 // gate_up: [rows, 2*inter] with gate first (mstar/model/components/distributed/
-// mlp.py:78-81); out: [rows, inter].  silu(x) = x / (1 + exp(-x)) in float.
+// mlp.py:78-81); out: [rows, inter].  silu(x) = x / (1 + exp(-x)), or the tanh form of gelu,
+// in float.
+// kind 0: relu(x)^2, 1: gelu (tanh form), 2: silu.
+__device__ __forceinline__ float plain_activation(float v, int kind) {
+    if (kind == 0) {
+        const float r = fmaxf(v, 0.f);
+        return r * r;
+    }
+    if (kind == 1)
+        return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v / (1.f + expf(-v));
+}
+
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int inter,
-                                size_t total) {
+                                size_t total, int kind) {
     gate_up = pdl_after(gate_up, pdl_wait());
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
@@ -255,24 +267,24 @@ __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ o
         const A* p = gate_up + row * 2 * (size_t)inter;
         const float g = to_float(p[col]);
         const float u = to_float(p[inter + col]);
-        const float act = g / (1.f + expf(-g));
-        out[idx] = from_float<A>(act * u);
+        out[idx] = from_float<A>(plain_activation(g, kind) * u);
     }
 }
 
 MSTAR_API int mstar_silu_mul(const void* gate_up, void* out, int act_dtype, int rows, int inter,
-                             void* stream) {
+                             int kind, void* stream) {
     const size_t total = (size_t)rows * inter;
     if (total == 0) return 0;
+    if (kind != 1 && kind != 2) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
     const size_t most = (size_t)device_sm_count() * 32;   // a grid-stride loop takes the rest
     if (blocks > most) blocks = most;
     if (act_dtype == MSTAR_F32)
-        mstar_launch((silu_mul_kernel<float>), dim3((int)blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, total);
+        mstar_launch((silu_mul_kernel<float>), dim3((int)blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, total, kind);
     else
-        mstar_launch((silu_mul_kernel<bf16>), dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, total);
+        mstar_launch((silu_mul_kernel<bf16>), dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, total, kind);
     return launch_status();
 }
 
@@ -704,16 +716,7 @@ MSTAR_API int mstar_mean2_postnorm(float* resid, const void* x0, const void* x1,
 }
 
 // ------------------------------------------------------------ activations without a gate
-// kind 0: relu(x)^2, 1: gelu (tanh form), 2: silu.  In place or not.
-__device__ __forceinline__ float plain_activation(float v, int kind) {
-    if (kind == 0) {
-        const float r = fmaxf(v, 0.f);
-        return r * r;
-    }
-    if (kind == 1)
-        return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    return v / (1.f + expf(-v));
-}
+// kinds as in plain_activation above.  In place or not.
 
 template <typename A>
 __global__ void activation_kernel(const A* __restrict__ x, A* __restrict__ out, size_t total,
@@ -771,5 +774,51 @@ MSTAR_API int mstar_sigmoid_gate_mul(void* y, const void* gate, int act_dtype, i
     else
         mstar_launch((sigmoid_gate_mul_kernel<bf16>), dim3(blocks), dim3(threads), 0, s, (bf16*)y,
                      (const bf16*)gate, cols, ldg, total);
+    return launch_status();
+}
+
+// ------------------------------------------------------------ out = y * sigmoid(gate of the head)
+// y: [rows, heads * dim] contiguous, in In; gate: one number per row and head, rows of `ldg`
+// elements (a view into a wider product), in G; out: [rows, heads * dim] in Out (may be y).
+template <typename In, typename Out, typename G>
+__global__ void head_gate_mul_kernel(const In* y, Out* out, const G* __restrict__ gate, int heads,
+                                     int dim, int ldg, size_t total) {
+    const unsigned long long waited = pdl_wait();
+    y = pdl_after(y, waited);
+    gate = pdl_after(gate, waited);
+    const int cols = heads * dim;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = idx / cols;
+        const int h = (int)(idx - r * cols) / dim;
+        const float g = to_float(gate[r * (size_t)ldg + h]);
+        out[idx] = from_float<Out>(to_float(y[idx]) / (1.f + expf(-g)));
+    }
+}
+
+MSTAR_API int mstar_head_gate_mul(const void* y, int in_dtype, void* out, int out_dtype,
+                                  const void* gate, int gate_dtype, int ldg, int rows, int heads,
+                                  int dim, void* stream) {
+    if (rows <= 0 || heads <= 0 || dim <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t total = (size_t)rows * heads * dim;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 4096 ? (total + threads - 1) / threads : 4096);
+#define GO(I, O, G)                                                                               \
+    mstar_launch((head_gate_mul_kernel<I, O, G>), dim3(blocks), dim3(threads), 0, s, (const I*)y, \
+                 (O*)out, (const G*)gate, heads, dim, ldg, total)
+    const int key = (in_dtype == MSTAR_F32 ? 4 : 0) | (out_dtype == MSTAR_F32 ? 2 : 0) |
+                    (gate_dtype == MSTAR_F32 ? 1 : 0);
+    switch (key) {
+        case 0: GO(bf16, bf16, bf16); break;
+        case 1: GO(bf16, bf16, float); break;
+        case 2: GO(bf16, float, bf16); break;
+        case 3: GO(bf16, float, float); break;
+        case 4: GO(float, bf16, bf16); break;
+        case 5: GO(float, bf16, float); break;
+        case 6: GO(float, float, bf16); break;
+        default: GO(float, float, float); break;
+    }
+#undef GO
     return launch_status();
 }

@@ -111,15 +111,23 @@ def gather_add_rows(resid: torch.Tensor, delta, rows: torch.Tensor):
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out=None):
-    """silu(gate_up[:, :I]) * gate_up[:, I:]."""
+GATE_ACTIVATIONS = {"gelu_tanh": 1, "silu": 2}
+
+
+def silu_mul(gate_up: torch.Tensor, out=None, kind: str = "silu"):
+    """act(gate_up[:, :I]) * gate_up[:, I:], act the SiLU or (``kind`` "gelu_tanh") the tanh
+    form of gelu."""
     _need_cuda(gate_up)
+    if kind not in GATE_ACTIVATIONS:
+        raise KernelError(f"gate activation {kind!r} has no kernel (known: "
+                          f"{sorted(GATE_ACTIVATIONS)})")
     assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
     rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
     if out is None:
         out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
     check(lib.get("elementwise").mstar_silu_mul(
-        gate_up.data_ptr(), out.data_ptr(), _dt(gate_up), rows, inter, _stream()), "silu_mul")
+        gate_up.data_ptr(), out.data_ptr(), _dt(gate_up), rows, inter, GATE_ACTIVATIONS[kind],
+        _stream()), "silu_mul")
     return out
 
 
@@ -662,16 +670,20 @@ def linear_act(x: torch.Tensor, w: torch.Tensor, kind: str, static_weights: bool
     return activation(linear(x, w, static_weights=static_weights), kind)
 
 
-def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = False):
-    """silu(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu]: one kernel for few
-    bfloat16 rows, else the product followed by the SiLU-multiply kernel."""
+def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = False,
+             kind: str = "silu"):
+    """act(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu], act the SiLU or (``kind``
+    "gelu_tanh") the tanh form of gelu: one kernel for few bfloat16 rows, else the product
+    followed by the activation-multiply kernel."""
     _need_cuda(x, w_gate_up)
-    if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
-        return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True, static_weights=static_weights)
-    if (_tc_ok(x, w_gate_up) and w_gate_up.shape[0] % 16 == 0
-            and tcgen05_tile(x.shape[0], w_gate_up.shape[0]) is not None):
-        return gemm_tcgen05_gated(x, w_gate_up)
-    return silu_mul(linear(x, w_gate_up))
+    if kind == "silu":
+        if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
+            return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True,
+                                static_weights=static_weights)
+        if (_tc_ok(x, w_gate_up) and w_gate_up.shape[0] % 16 == 0
+                and tcgen05_tile(x.shape[0], w_gate_up.shape[0]) is not None):
+            return gemm_tcgen05_gated(x, w_gate_up)
+    return silu_mul(linear(x, w_gate_up, static_weights=static_weights), kind=kind)
 
 
 _argmax_scratch: dict = {}
@@ -855,6 +867,22 @@ def sigmoid_gate_mul(y: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
     return y
 
 
+def head_gate_mul(y: torch.Tensor, gate: torch.Tensor, heads: int,
+                  out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """y[t, h, :] * sigmoid(gate[t, h]): one gate a head.  ``y``: [tokens, heads * dim]
+    contiguous (float or bfloat16), ``gate``: [tokens, heads], a column view of a wider product
+    (float or bfloat16).  In place when ``out_dtype`` is y's own type or None."""
+    _need_cuda(y, gate)
+    assert y.dim() == 2 and y.is_contiguous() and y.shape[1] % heads == 0
+    assert tuple(gate.shape) == (y.shape[0], heads) and gate.stride(1) == 1
+    out_dtype = out_dtype or y.dtype
+    out = y if out_dtype == y.dtype else torch.empty(y.shape, dtype=out_dtype, device=y.device)
+    check(lib.get("elementwise").mstar_head_gate_mul(
+        y.data_ptr(), _dt(y), out.data_ptr(), _dt(out), gate.data_ptr(), _dt(gate), gate.stride(0),
+        y.shape[0], heads, y.shape[1] // heads, _stream()), "head_gate_mul")
+    return out
+
+
 # ------------------------------------------------------------------ matrix memory
 def matrix_memory_state_size(heads: int, dim: int, vdim: int) -> int:
     """Floats of one request's state: S^T [heads, vdim, dim], n [heads, dim], m [heads]."""
@@ -902,27 +930,55 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, he
 
 
 # ------------------------------------------------------------------ latent attention
-def latent_fill(proj: torch.Tensor, dkv_offset: int, norm_weight: torch.Tensor, freq: torch.Tensor,
-                positions, cache_pos, token_req, block_table, cache: torch.Tensor, heads: int,
-                qk_dim: int, rot: int, rot_dims: int, rank: int, page_size: int, eps: float) -> None:
-    """Normalise the latent part of the down-projection, rotate the shared key part and write
-    both into the token's cache row; rotate the rotated part of every query head in place.
-    ``proj``: [tokens, ...] with the queries at column 0 (head by head: qk_dim plain, rot
-    rotated features) and the down-projection at ``dkv_offset``; ``cache``: [pages, 1, 1,
-    page_size, rank + rot]; ``freq``: float64 [rot_dims / 2]."""
-    _need_cuda(proj, norm_weight, freq, positions, cache_pos, token_req, block_table, cache)
-    assert proj.dim() == 2 and proj.stride(1) == 1 and cache.dtype == proj.dtype
-    assert cache.is_contiguous() and tuple(cache.shape[1:]) == (1, 1, page_size, rank + rot)
-    assert norm_weight.dtype == torch.float32 and norm_weight.numel() == rank
+def latent_fill(q, dkv, norm_weight, freq: torch.Tensor, positions, cache_pos, token_req,
+                block_table, cache, heads: int, qk_dim: int, rot: int, rot_dims: int, rank: int,
+                page_size: int, eps: float, interleaved: bool = True, q_latent=None,
+                q_latent_weight=None):
+    """The elementwise work around a latent attention's products, one launch; each job is
+    left out when its tensor is None.
+
+    ``dkv`` [tokens, rank + rot] (a column view; float or the cache's type): the latent part
+    is RMS-normed with ``norm_weight`` (float [rank]), the first ``rot_dims`` key features are
+    rotated, and the row goes into the token's slot of ``cache`` [pages, 1, 1, page_size,
+    rank + rot].  ``q`` [tokens, heads * (qk_dim + rot)] (the cache's type; a column view):
+    the rotated part of every head is rotated in place.  ``q_latent`` [tokens, q_rank] (a
+    column view, same type as ``dkv``): RMS-normed with ``q_latent_weight`` (float) into new
+    rows of the cache's type, which are returned.  Pairs are (2i, 2i+1) when ``interleaved``,
+    else (i, i + rot_dims/2); ``freq``: float64 [rot_dims / 2]."""
+    _need_cuda(q, dkv, norm_weight, freq, positions, cache_pos, token_req, block_table, cache,
+               q_latent, q_latent_weight)
     assert freq.dtype == torch.float64 and freq.numel() == rot_dims // 2
+    first = next(t for t in (q, dkv, q_latent) if t is not None)
+    tokens = first.shape[0]
+    act = q.dtype if q is not None else cache.dtype
+    ins = [t for t in (dkv, q_latent) if t is not None]
+    in_dtype = ins[0].dtype if ins else act
+    assert all(t.dtype == in_dtype and t.dim() == 2 and t.stride(1) == 1 for t in ins)
+    if q is not None:
+        assert q.dim() == 2 and q.stride(1) == 1 and q.shape[1] == heads * (qk_dim + rot)
+    if dkv is not None:
+        assert cache.dtype == act and dkv.shape[1] == rank + rot
+        assert cache.is_contiguous() and tuple(cache.shape[1:]) == (1, 1, page_size, rank + rot)
+        assert norm_weight.dtype == torch.float32 and norm_weight.numel() == rank
+    out = None
+    q_rank = 0
+    if q_latent is not None:
+        q_rank = q_latent.shape[1]
+        assert q_latent_weight.dtype == torch.float32 and q_latent_weight.numel() == q_rank
+        out = torch.empty((tokens, q_rank), dtype=act, device=q_latent.device)
     code = lib.get("attention_latent").mstar_latent_fill(
-        proj.data_ptr(), _dt(proj), proj.stride(0), dkv_offset, norm_weight.data_ptr(),
+        _ptr(q), q.stride(0) if q is not None else 0, _ptr(dkv),
+        dkv.stride(0) if dkv is not None else 0, _DT[in_dtype], _DT[act], _ptr(norm_weight),
         freq.data_ptr(), positions.data_ptr(), cache_pos.data_ptr(), token_req.data_ptr(),
-        block_table.data_ptr(), block_table.stride(0), cache.data_ptr(), proj.shape[0], heads,
-        qk_dim, rot, rot_dims, rank, page_size, float(eps), _stream())
+        _ptr(block_table), block_table.stride(0) if block_table is not None else 0, _ptr(cache),
+        _ptr(q_latent), q_latent.stride(0) if q_latent is not None else 0, _ptr(q_latent_weight),
+        _ptr(out), q_rank, q_rank, tokens, heads, qk_dim, rot, rot_dims, rank, page_size,
+        int(interleaved), float(eps), _stream())
     if code == -1:
-        raise KernelError(f"latent cache fill refuses rot_dims={rot_dims} of rot={rot}")
+        raise KernelError(f"latent cache fill refuses rot_dims={rot_dims} of rot={rot}, or float "
+                          "activations with inputs of another type")
     check(code, "latent_fill")
+    return out
 
 
 def latent_attention_plan(tokens: int, heads: int, rank: int, max_keys: int,
@@ -1126,25 +1182,44 @@ def sink_page_elements(num_kv_heads: int, page_size: int, head_dim: int, v_dim: 
 def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache_pos, token_req,
                  block_table, kv_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
                  head_dim: int, v_dim: int, rot: int, page_size: int, eps: float,
-                 out_dtype: torch.dtype) -> torch.Tensor:
+                 out_dtype: torch.dtype, conv=None, value_from_key: bool = False) -> torch.Tensor:
     """From the float fused projection ``qkv`` [tokens, (heads + kv_heads) * head_dim +
-    kv_heads * v_dim]: add ``bias``, norm every query and key head (``q_norm`` / ``k_norm``
-    weights of ``head_dim``, or None for no norm), rotate their first ``rot`` features
-    (``freq``: float64 [rot / 2]), write keys and values into the token's cache page, and
-    return the queries [tokens, heads * head_dim] in ``out_dtype``."""
+    kv_heads * v_dim (+ columns this kernel does not read)]: add ``bias``, norm every query
+    and key head (``q_norm`` / ``k_norm`` weights of ``head_dim``, or None for no norm), rotate
+    their first ``rot`` features (``freq``: float64 [rot / 2]), write keys and values into the
+    token's cache page, and return the queries [tokens, heads * head_dim] in ``out_dtype``.
+
+    ``conv``: (q weights [heads * head_dim, taps], k weights [kv_heads * head_dim, taps],
+    qo_indptr, slots, state) puts a causal convolution over time on every q and k channel
+    before the norm; the rows before a portion come from ``state`` [slots, (taps - 1) *
+    channels] (float), which ``conv_state_advance`` moves on afterwards.  ``value_from_key``:
+    the row has no value part; a key head before its norm is the value head."""
     _need_cuda(qkv, bias, q_norm, k_norm, freq, positions, cache_pos, token_req, block_table,
                kv_cache)
-    assert qkv.dtype == torch.float32 and qkv.is_contiguous() and kv_cache.is_contiguous()
+    assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
+    assert kv_cache.is_contiguous()
     tokens = qkv.shape[0]
-    assert qkv.shape[1] == (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_dim
+    need = (num_heads + num_kv_heads) * head_dim + (0 if value_from_key else num_kv_heads * v_dim)
+    assert qkv.shape[1] >= need
     assert kv_cache.dtype == out_dtype
     assert kv_cache[0].numel() == sink_page_elements(num_kv_heads, page_size, head_dim, v_dim)
     assert (q_norm is None) == (k_norm is None)
+    wq = wk = qo = slots = state = None
+    taps = 0
+    if conv is not None:
+        wq, wk, qo, slots, state = conv
+        _need_cuda(wq, wk, qo, slots, state)
+        taps = wq.shape[1]
+        assert tuple(wq.shape) == (num_heads * head_dim, taps) and wq.is_contiguous()
+        assert tuple(wk.shape) == (num_kv_heads * head_dim, taps) and wk.is_contiguous()
+        if taps > 1:
+            assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+            assert state.shape[1] >= (taps - 1) * (num_heads + num_kv_heads) * head_dim
     wd = F32
-    for w in (bias, q_norm, k_norm):
+    for w in (bias, q_norm, k_norm, wq, wk):
         if w is not None:
             wd = _dt(w)
-    for w in (bias, q_norm, k_norm):
+    for w in (bias, q_norm, k_norm, wq, wk):
         assert w is None or (_dt(w) == wd and w.is_contiguous())
     if rot:
         assert freq is not None and freq.dtype == torch.float64 and freq.numel() == rot // 2
@@ -1154,12 +1229,29 @@ def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache
         positions.data_ptr(), cache_pos.data_ptr(), token_req.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), q.data_ptr(), kv_cache.data_ptr(), _DT[out_dtype], tokens, num_heads,
         num_kv_heads, head_dim, v_dim, rot, page_size, float(eps), int(q_norm is not None),
-        _stream())
+        qkv.stride(0), _ptr(wq), _ptr(wk), taps, int(value_from_key), _ptr(qo), _ptr(slots),
+        _ptr(state) if taps > 1 else 0, state.stride(0) if taps > 1 else 0, _stream())
     if code == -1:
         raise KernelError(f"attention input kernel refuses head_dim={head_dim}, v_dim={v_dim}, "
-                          f"rot={rot}")
+                          f"rot={rot}, taps={taps}")
     check(code, "sink_prepare")
     return q
+
+
+def conv_state_advance(qkv: torch.Tensor, channels: int, taps: int, qo_indptr, slots,
+                       state: torch.Tensor, entries: int) -> None:
+    """After ``sink_prepare`` with a convolution: every entry's slot takes the last
+    ``taps - 1`` rows of the first ``channels`` columns of its sequence (what the slot held
+    moves up where the portion is shorter)."""
+    if taps <= 1:
+        return
+    _need_cuda(qkv, qo_indptr, slots, state)
+    assert qkv.dtype == torch.float32 and qkv.stride(1) == 1 and qkv.shape[1] >= channels
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    assert state.shape[1] >= (taps - 1) * channels
+    check(lib.get("attention_sink").mstar_conv_state_advance(
+        qkv.data_ptr(), qkv.stride(0), channels, taps, qo_indptr.data_ptr(), slots.data_ptr(),
+        state.data_ptr(), state.stride(0), entries, _stream()), "conv_state_advance")
 
 
 def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_heads: int,

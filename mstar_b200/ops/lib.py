@@ -23,7 +23,7 @@ _SIGNATURES = {
         "mstar_scale_softcap": [_vp, _ll, _f, _f, _vp],
         "mstar_add_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _i, _vp],
         "mstar_gather_add_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
-        "mstar_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+        "mstar_silu_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
         "mstar_convert": [_vp, _i, _vp, _i, _ll, _vp],
         "mstar_rope_kv_write": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
                                 _i, _i, _vp],
@@ -35,6 +35,7 @@ _SIGNATURES = {
         "mstar_mean2_postnorm": [_vp, _vp, _vp, _vp, _vp, _f, _vp, _f, _f, _f, _vp, _i, _i, _i,
                                  _vp],
         "mstar_sigmoid_gate_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
+        "mstar_head_gate_mul": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
     },
     "matrix_memory": {
         "mstar_matrix_memory_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i,
@@ -44,8 +45,8 @@ _SIGNATURES = {
     "attention_latent": {
         "mstar_latent_attention": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
                                    _i, _i, _f, _i, _i, _i, _vp, _vp],
-        "mstar_latent_fill": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i,
-                              _i, _i, _i, _i, _f, _vp],
+        "mstar_latent_fill": [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp,
+                              _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     },
     "routed_experts": {
         "mstar_route_topk": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
@@ -56,7 +57,9 @@ _SIGNATURES = {
     },
     "attention_sink": {
         "mstar_sink_prepare": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i,
-                               _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp],
+                               _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _i, _i, _vp, _vp,
+                               _vp, _ll, _vp],
+        "mstar_conv_state_advance": [_vp, _i, _i, _i, _vp, _vp, _vp, _ll, _i, _vp],
         "mstar_sink_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
                                          _i, _i, _i, _f, _i, _vp],
     },

@@ -14,7 +14,10 @@ Beyond that plain form a spec may ask for biases on q, k and v, an RMS norm per 
 key head before the position encoding, a value size other than the key size, and a window
 that keeps the sequence's first keys visible (``keep_first``).  Such a layer takes the fused
 product in float, a kernel that adds the bias, norms, rotates and fills the cache pages, and
-an attention kernel that walks the kept first keys and the window's keys.
+an attention kernel that walks the kept first keys and the window's keys.  The same path
+takes a short causal convolution over time on the q and k channels (its last inputs are
+per-request state in a slot), values that are the keys before their norm, and one sigmoid
+gate a head on the output; the gate's rows ride in the fused first product.
 """
 from __future__ import annotations
 
@@ -22,7 +25,7 @@ import torch
 
 from .. import ops
 from ..weights.names import ParamSpec
-from .base import CacheNeed, KVNeed, LayerCache, Runtime, StepContext
+from .base import CacheNeed, KVNeed, LayerCache, Runtime, StateNeed, StepContext
 from .registry import build_part, register_part
 
 
@@ -35,7 +38,10 @@ class Attention:
     @classmethod
     def param_specs(cls, spec) -> dict:
         q_rows = spec.num_heads * spec.head_dim
-        kv_rows = spec.num_kv_heads * (spec.head_dim + spec.value_dim)
+        kv_rows = spec.num_kv_heads * (spec.head_dim + (0 if spec.value_from_key
+                                                        else spec.value_dim))
+        if spec.head_gate:
+            kv_rows += spec.num_heads           # the gate's rows come last
         if spec.shares_kv:
             first = {"q.weight": ParamSpec((q_rows, spec.hidden_size))}
         else:
@@ -45,16 +51,24 @@ class Attention:
         if spec.qk_norm_eps is not None:
             first["q_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
             first["k_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
+        if spec.conv_taps:
+            first["q_conv.weight"] = ParamSpec((q_rows, spec.conv_taps), role="vector")
+            first["k_conv.weight"] = ParamSpec((spec.num_kv_heads * spec.head_dim, spec.conv_taps),
+                                               role="vector")
         first["o.weight"] = ParamSpec((spec.hidden_size, spec.num_heads * spec.value_dim))
         return first
 
     @classmethod
     def cache_need(cls, spec) -> CacheNeed:
+        state = None
+        if spec.conv_taps > 1:                  # the convolution's last inputs, q then k channels
+            channels = (spec.num_heads + spec.num_kv_heads) * spec.head_dim
+            state = StateNeed(shape=((spec.conv_taps - 1) * channels,), dtype="float32")
         return CacheNeed(kv=KVNeed(num_kv_heads=spec.num_kv_heads, head_dim=spec.head_dim,
                                    window=spec.window, keep_first=spec.keep_first if spec.window
                                    else 0,
                                    v_head_dim=None if spec.value_dim == spec.head_dim
-                                   else spec.value_dim))
+                                   else spec.value_dim), state=state)
 
     def __init__(self, spec, params: dict, runtime: Runtime):
         if spec.num_heads % spec.num_kv_heads:
@@ -70,6 +84,17 @@ class Attention:
         self.w_out = params["o.weight"]
         self.bias = params.get("qkv.bias")
         self.q_norm, self.k_norm = params.get("q_norm.weight"), params.get("k_norm.weight")
+        self.q_conv, self.k_conv = params.get("q_conv.weight"), params.get("k_conv.weight")
+        if spec.value_from_key and spec.value_dim != spec.head_dim:
+            raise ValueError("values that are the keys have the keys' size")
+        if spec.conv_taps and spec.bias:
+            raise ValueError("a convolution on biased projections is not defined here")
+        small = [w for w in (self.bias, self.q_norm, self.k_norm, self.q_conv, self.k_conv)
+                 if w is not None]
+        if len({w.dtype for w in small}) > 1:   # the input kernel takes them in one type
+            self.bias, self.q_norm, self.k_norm, self.q_conv, self.k_conv = (
+                None if w is None else w.float().contiguous()
+                for w in (self.bias, self.q_norm, self.k_norm, self.q_conv, self.k_conv))
         if not spec.plain:
             from .rope import rope_inverse_frequencies
 
@@ -108,14 +133,24 @@ class Attention:
     def _forward_general(self, x, ctx: StepContext, cache: LayerCache):
         s = self.spec
         qkv = ops.linear(x, self.w_in, out_dtype=torch.float32, static_weights=True)
+        conv = None
+        if s.conv_taps:
+            conv = (self.q_conv, self.k_conv, ctx.qo_indptr, ctx.slots, cache.state)
         q = ops.sink_prepare(qkv, self.bias, self.q_norm, self.k_norm, self.freq, ctx.positions,
                              ctx.cache_pos, ctx.token_req, cache.block_table, cache.kv,
                              s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, self.rot,
-                             cache.page_size, s.qk_norm_eps or 0.0, self.runtime.dtype)
+                             cache.page_size, s.qk_norm_eps or 0.0, self.runtime.dtype,
+                             conv=conv, value_from_key=s.value_from_key)
+        if s.conv_taps > 1:
+            ops.conv_state_advance(qkv, (s.num_heads + s.num_kv_heads) * s.head_dim, s.conv_taps,
+                                   ctx.qo_indptr, ctx.slots, cache.state, ctx.num_entries)
         out = ops.sink_attention(q, cache.kv, cache.block_table, ctx.token_req, ctx.cache_pos,
                                  s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
                                  cache.page_size, s.window or 0, s.keep_first if s.window else 0,
                                  self.scale, ctx=ctx)
+        if s.head_gate:
+            gate_at = qkv.shape[1] - s.num_heads
+            ops.head_gate_mul(out, qkv[:, gate_at:], s.num_heads)
         return ops.linear(out, self.w_out, static_weights=True)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:

@@ -1,5 +1,6 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)) with one fused [gate; up] matrix
-(mstar/model/components/distributed/mlp.py:78-81; gate is shard 0, up shard 1)."""
+(mstar/model/components/distributed/mlp.py:78-81; gate is shard 0, up shard 1); act is the
+SiLU or the tanh form of gelu."""
 from __future__ import annotations
 
 from .. import ops
@@ -19,16 +20,17 @@ class GatedMLP:
         }
 
     def __init__(self, spec, params: dict, runtime: Runtime):
-        if spec.activation != "silu":
-            raise ValueError(f"gated_mlp activation {spec.activation!r} has no kernel (silu has)")
+        if spec.activation not in ops.GATE_ACTIVATIONS:
+            raise ValueError(f"gated_mlp activation {spec.activation!r} has no kernel "
+                             f"({sorted(ops.GATE_ACTIVATIONS)} have)")
         self.spec = spec
         self.runtime = runtime
         self.gate_up = params["gate_up.weight"]
         self.down = params["down.weight"]
 
     def forward(self, x, ctx):
-        return ops.linear(ops.gated_up(x, self.gate_up, static_weights=True), self.down,
-                          static_weights=True)
+        return ops.linear(ops.gated_up(x, self.gate_up, static_weights=True,
+                                       kind=self.spec.activation), self.down, static_weights=True)
 
 
 class MLP:
