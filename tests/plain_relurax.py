@@ -82,8 +82,10 @@ def plain_causal_conv(u, weight, before):
     return y, full[full.shape[0] - (taps - 1):]
 
 
-def plain_window_visible(i, j, size):
-    return 0 <= i - j < size
+def plain_window_visible(i, j, size=None):
+    """Whether position i sees position j: itself and the size - 1 before it (all before it
+    without a size)."""
+    return j <= i and (size is None or i - j < size)
 
 
 def plain_dense_ff(h, w_gate, w_up, w_down):
@@ -119,7 +121,7 @@ def plain_conv_attention(h, w, m, eps, state):
     gate = plain_sigmoid(h @ np.asarray(w["g"], F).T)         # [tokens, heads]
     out = np.zeros((n, heads, dim), F)
     per = heads // groups
-    size = m["mask"]["size"]
+    size = m["mask"]["size"] if m.get("mask") else None
     for t in range(n):
         i = start + t
         js = [j for j in range(i + 1) if plain_window_visible(i, j, size)]
