@@ -422,6 +422,8 @@ def arch_bench(args) -> int:
 
     if args.arch == "vudivik":
         return vudivik_bench(args)
+    if args.arch == "relurax":
+        return relurax_bench(args)
     pk = peaks()
     t_cfg, l_cfg = tifosun_sizes(args.arch_size)
     page, batch = args.page_size, args.batch
@@ -732,6 +734,234 @@ def vudivik_bench(args) -> int:
     return 0
 
 
+def relurax_sizes(name: str) -> tuple:
+    """(Relurax config, Llama config of equal size) at layer sizes that resemble a real model's: three sliding-window layers (keys
+    through a four-tap convolution, values that are the keys, a gate a head) to one latent
+    layer with queries through a latent of their own, the second latent layer reading the
+    first one's rows; gelu-gated feed-forwards.  The Llama beside it has the same width,
+    depth, vocabulary, heads, key/value heads and feed-forward size."""
+    if name == "small":
+        width, depth, vocab, ff = 1024, 8, 32000, 2816
+        att = dict(heads=8, kv_heads=2, dim=128, vdim=128, conv=4, mask={"size": 1024},
+                   scale=128 ** -0.5)
+        lat = dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=256, q_rank=384,
+                   rot={"base": 500000.0, "dims": 32}, scale=96 ** -0.5)
+    elif name == "medium":
+        width, depth, vocab, ff = 2048, 12, 64000, 5632
+        att = dict(heads=16, kv_heads=4, dim=128, vdim=128, conv=4, mask={"size": 1024},
+                   scale=128 ** -0.5)
+        lat = dict(heads=16, dim=128, rot_dim=64, vdim=128, kv_rank=512, q_rank=1024,
+                   rot={"base": 500000.0, "dims": 64}, scale=192 ** -0.5)
+    else:
+        raise ValueError(f"unknown size {name!r} (small, medium)")
+    layers, first_latent = [], None
+    for i in range(depth):
+        if i % 4 == 2:
+            m = dict(lat)
+            if first_latent is None:
+                first_latent = i
+            else:
+                m["kv_from"] = first_latent
+            layers.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            layers.append({"type": "attention", "mixer": dict(att), "mlp": {"kind": "dense", "ff": ff}})
+    relurax = {"architecture": "Relurax", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+               "layers": layers}
+    llama = dict(ORPHEUS_3B, num_hidden_layers=depth, hidden_size=width,
+                 num_attention_heads=att["heads"], num_key_value_heads=att["kv_heads"],
+                 head_dim=128, intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False)
+    return relurax, llama
+
+
+def relurax_bench(args) -> int:
+    """``--arch relurax``: prefill and decode throughput of the Relurax decoder (random
+    weights, bfloat16) beside the Llama decoder at equal size, through the same step
+    function; then the kernels of its two mixers alone at the sizes of one layer, each beside
+    the like kernel of the decoder that is closest to it (window attention and its input
+    kernel: Vudivik's form of the same kernels and the Llama attention; latent attention:
+    Tifosun's windowed form), with what each has to move or compute against the measured
+    peaks.  One JSON line."""
+    import torch
+
+    from mstar_b200 import ops
+    from mstar_b200.parts.base import StepContext
+
+    pk = peaks()
+    r_cfg, l_cfg = relurax_sizes(args.arch_size)
+    page, batch = args.page_size, args.batch
+    out = {"arch": "Relurax", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "models": {}, "kernels": {}}
+    _time_models(args, (("relurax", r_cfg), ("llama", l_cfg)), out)
+
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=g, device=dev)).to(torch.bfloat16)
+
+    def i32(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def record(name, ms, nbytes=None, flops=None, **more):
+        row = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            row["gbs"] = round(nbytes / ms / 1e6, 1)
+            row["frac_hbm"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)
+        if flops is not None:
+            row["tflops"] = round(flops / ms / 1e9, 2)
+            row["frac_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 5)
+        row.update(more)
+        out["kernels"][name] = row
+
+    width = r_cfg["width"]
+    att = next(l["mixer"] for l in r_cfg["layers"] if l["type"] == "attention")
+    lat = next(l["mixer"] for l in r_cfg["layers"] if l["type"] == "latent_attention")
+    H, G, hd, taps, window = att["heads"], att["kv_heads"], att["dim"], att["conv"], att["mask"]["size"]
+    ctx_len = PROMPT_LEN
+    pages_per = -(-ctx_len // page)
+    channels = (H + G) * hd
+    for tokens, reqs, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        per = tokens // reqs
+        seen = min(ctx_len, window + per)
+        copies = 1 if label == "prefill" else max(1, -(-(160 << 20) // (reqs * seen * G * hd * 4)))
+        caches = [rnd(reqs * pages_per + 1, 2, G, page, hd) for _ in range(copies)]
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        token_req = i32([r for r in range(reqs) for _ in range(per)])
+        cache_pos = i32([ctx_len - per + k for _ in range(reqs) for k in range(per)])
+        indptr = i32([k * per for k in range(reqs + 1)])
+        kv_len = i32([ctx_len] * reqs)
+        slots = i32(list(range(reqs)))
+        q = rnd(tokens, H * hd)
+        sc = StepContext(num_tokens=tokens, num_entries=reqs, token_req=token_req,
+                         positions=cache_pos, cache_pos=cache_pos, qo_indptr=indptr, kv_len=kv_len,
+                         slots=slots, q_lens=[per] * reqs, kv_lens=[ctx_len] * reqs,
+                         host_slots=list(range(reqs)), max_q_len=per, max_kv_len=ctx_len,
+                         num_decode=reqs if per == 1 else 0)
+        turn = {"i": 0}
+
+        def attend(keep=0):
+            c = caches[turn["i"] % copies].view(reqs * pages_per + 1, -1)
+            turn["i"] += 1
+            return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, window,
+                                      keep, att["scale"], ctx=sc)
+
+        reps = max(copies, 4) if label == "decode" else 2
+        keys = sum(min(ctx_len - per + k + 1, window) for k in range(per)) * reqs
+        ms = _time_graph(attend, reps=reps)
+        record(f"window_attention_{label}", ms, nbytes=reqs * seen * G * hd * 4.0,
+               flops=4.0 * H * keys * hd)
+        # the same kernel as the Vudivik decoder runs it: four kept first keys beside the window
+        ms = _time_graph(lambda: attend(4), reps=reps)
+        record(f"vudivik_window_attention_{label}", ms, nbytes=reqs * (seen + 4) * G * hd * 4.0,
+               flops=4.0 * H * (keys + 4 * tokens) * hd)
+        # what comes before it: convolution over q and k, head norms, cache write (values are
+        # the keys before their norm) ...
+        qkv = torch.randn(tokens, channels + H, device=dev)
+        state = torch.zeros(reqs, (taps - 1) * channels, device=dev)
+        wq, wk = rnd(H * hd, taps), rnd(G * hd, taps)
+        nq, nk = rnd(hd), rnd(hd)
+        c0 = caches[0].view(reqs * pages_per + 1, -1)
+        ms = _time_graph(lambda: ops.sink_prepare(
+            qkv, None, nq, nk, None, cache_pos, cache_pos, token_req, table, c0, H, G, hd, hd, 0,
+            page, 1e-5, torch.bfloat16, conv=(wq, wk, indptr, slots, state), value_from_key=True),
+            reps=8)
+        record(f"conv_norm_cache_{label}", ms,
+               nbytes=tokens * (channels * 4 + H * hd * 2 + 2 * G * hd * 2.0))
+        ms = _time_graph(lambda: ops.conv_state_advance(qkv, channels, taps, indptr, slots, state,
+                                                        reqs), reps=8)
+        record(f"conv_rows_advance_{label}", ms, nbytes=reqs * (taps - 1) * channels * 8.0)
+        # ... beside the Vudivik decoder's form of that kernel: bias, head norms, rotation,
+        # separate values
+        qkv_v = torch.randn(tokens, (H + 2 * G) * hd, device=dev)
+        bias = rnd((H + 2 * G) * hd)
+        freq = torch.rand(hd // 2, dtype=torch.float64, device=dev)
+        ms = _time_graph(lambda: ops.sink_prepare(
+            qkv_v, bias, nq, nk, freq, cache_pos, cache_pos, token_req, table, c0, H, G, hd, hd,
+            hd, page, 1e-5, torch.bfloat16), reps=8)
+        record(f"vudivik_bias_norm_rope_cache_{label}", ms,
+               nbytes=tokens * ((H + 2 * G) * hd * 4 + H * hd * 2 + 2 * G * hd * 2.0))
+        o = rnd(tokens, H * hd)
+        ms = _time_graph(lambda: ops.head_gate_mul(o, qkv[:, channels:], H), reps=8)
+        record(f"head_gate_{label}", ms, nbytes=tokens * (H * hd * 4.0 + H * 4))
+        # the Llama decoder's attention on the same cache: every key (no window)
+        out_l = torch.empty(tokens, H * hd, dtype=torch.bfloat16, device=dev)
+        turn["i"] = 0
+        if label == "decode":
+            def llama_attend():
+                c = caches[turn["i"] % copies]
+                turn["i"] += 1
+                ops.paged_decode_attention(q, q.stride(0), out_l, c, table, token_req, cache_pos,
+                                           tokens, H, G, hd, page, 0, att["scale"], ctx_len)
+            all_keys, all_bytes = reqs * ctx_len, reqs * ctx_len * G * hd * 4.0
+        else:
+            def llama_attend():
+                ops.paged_prefill_attention(q, q.stride(0), out_l, caches[0], table, indptr, kv_len,
+                                            0, reqs, per, H, G, hd, page, 0, att["scale"])
+            all_keys, all_bytes = per * (per + 1) // 2, ctx_len * G * hd * 4.0
+        ms = _time_graph(llama_attend, reps=reps)
+        record(f"llama_attention_{label}", ms, nbytes=all_bytes, flops=4.0 * H * all_keys * hd)
+
+    heads, rank, rot, q_rank = lat["heads"], lat["kv_rank"], lat["rot_dim"], lat["q_rank"]
+    dim = lat["dim"]
+    for tokens, reqs, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        per = tokens // reqs
+        copies = 1 if label == "prefill" else max(1, -(-(160 << 20) // (reqs * ctx_len * (rank + rot) * 2)))
+        caches = [rnd(reqs * pages_per + 1, 1, 1, page, rank + rot) for _ in range(copies)]
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        token_req = i32([r for r in range(reqs) for _ in range(per)])
+        cache_pos = i32([ctx_len - per + k for _ in range(reqs) for k in range(per)])
+        q_abs = torch.randn(tokens, heads, rank, device=dev)
+        q_rot = rnd(tokens, heads, rot)
+        turn = {"i": 0}
+
+        def latent(win=0):
+            c = caches[turn["i"] % copies]
+            turn["i"] += 1
+            return ops.latent_attention(q_abs, q_rot, c, table, token_req, cache_pos, heads, rank,
+                                        rot, page, win, lat["scale"], max_keys=ctx_len)
+
+        reps = max(copies, 4) if label == "decode" else 2
+        for name, win in (("latent_attention", 0), ("tifosun_latent_attention_window_512", 512)):
+            seen = ctx_len if not win else min(ctx_len, win + per)
+            keys = sum(min(ctx_len - per + k + 1, win or ctx_len) for k in range(per)) * reqs
+            ms = _time_graph(lambda: latent(win), reps=reps)
+            record(f"{name}_{label}", ms, nbytes=reqs * seen * (rank + rot) * 2.0,
+                   flops=2.0 * heads * keys * (2 * rank + rot))
+        # the elementwise work around the products: both latents normed, the shared key part
+        # rotated, the cache row written; then the rotation of the queries
+        down = torch.randn(tokens, q_rank + rank + rot + heads, device=dev)
+        wn, wqn = torch.randn(rank, device=dev), torch.randn(q_rank, device=dev)
+        freq = torch.rand(rot // 2, dtype=torch.float64, device=dev)
+        fill = dict(positions=cache_pos, cache_pos=cache_pos, token_req=token_req,
+                    block_table=table, heads=heads, qk_dim=dim, rot=rot, rot_dims=rot, rank=rank,
+                    page_size=page, eps=1e-5, interleaved=False)
+        ms = _time_graph(lambda: ops.latent_fill(None, down[:, q_rank:q_rank + rank + rot], wn, freq,
+                                                 cache=caches[0], q_latent=down[:, :q_rank],
+                                                 q_latent_weight=wqn, **fill), reps=8)
+        record(f"latent_norms_rope_cache_{label}", ms,
+               nbytes=tokens * ((q_rank + rank + rot) * 4 + (q_rank + rank + rot) * 2.0))
+        qs = rnd(tokens, heads * (dim + rot))
+        ms = _time_graph(lambda: ops.latent_fill(qs, None, None, freq, cache=caches[0], **fill), reps=8)
+        record(f"latent_query_rope_{label}", ms, nbytes=tokens * heads * rot * 4.0)
+    ff = r_cfg["layers"][0]["mlp"]["ff"]
+    w_gu = rnd(2 * ff, width, scale=0.02)
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        x = rnd(tokens, width)
+        for kind in ("gelu_tanh", "silu"):
+            ms = _time_graph(lambda: ops.gated_up(x, w_gu, static_weights=True, kind=kind), reps=8)
+            record(f"gated_up_{kind}_{label}", ms, nbytes=2.0 * ff * width * 2,
+                   flops=2.0 * tokens * 2 * ff * width)
+        resid = torch.randn(tokens, width, device=dev)
+        delta, w = rnd(tokens, width), rnd(width)
+        wb = torch.randn(width, device=dev)
+        ms = _time_graph(lambda: ops.add_postnorm_rmsnorm(resid, delta, wb, 1e-5, 0.0, w, 1e-5, 0.0,
+                                                          torch.bfloat16), reps=20)
+        record(f"postnorm_add_norm_{label}", ms, nbytes=tokens * width * (4 + 4 + 2 + 2.0))
+    ops.check_error_word(dev)
+    print(json.dumps(out))
+    return 0
+
+
 # --------------------------------------------------------------- single kernels
 def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
     """Median milliseconds of one call of ``fn`` when ``reps`` calls are replayed as one
@@ -975,7 +1205,7 @@ def main() -> int:
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),
                     help="layer sizes; the default is the benchmark model")
-    ap.add_argument("--arch", default=None, choices=["tifosun", "vudivik"],
+    ap.add_argument("--arch", default=None, choices=["tifosun", "vudivik", "relurax"],
                     help="measure another architecture beside the Llama decoder at equal size "
                          "(prefill, decode, its own kernels) instead of the headline workload")
     ap.add_argument("--arch-size", default="small", choices=["small", "medium"])
