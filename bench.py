@@ -838,12 +838,15 @@ def relurax_bench(args) -> int:
                          host_slots=list(range(reqs)), max_q_len=per, max_kv_len=ctx_len,
                          num_decode=reqs if per == 1 else 0)
         turn = {"i": 0}
+        qkv = torch.randn(tokens, channels + H, device=dev)     # the first product: [q | k | gate]
 
         def attend(keep=0):
             c = caches[turn["i"] % copies].view(reqs * pages_per + 1, -1)
             turn["i"] += 1
+            # the Relurax form gates every head where the output is written
             return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, window,
-                                      keep, att["scale"], ctx=sc)
+                                      keep, att["scale"], ctx=sc,
+                                      gate=None if keep else qkv[:, channels:])
 
         reps = max(copies, 4) if label == "decode" else 2
         keys = sum(min(ctx_len - per + k + 1, window) for k in range(per)) * reqs
@@ -856,7 +859,6 @@ def relurax_bench(args) -> int:
                flops=4.0 * H * (keys + 4 * tokens) * hd)
         # what comes before it: convolution over q and k, head norms, cache write (values are
         # the keys before their norm) ...
-        qkv = torch.randn(tokens, channels + H, device=dev)
         state = torch.zeros(reqs, (taps - 1) * channels, device=dev)
         wq, wk = rnd(H * hd, taps), rnd(G * hd, taps)
         nq, nk = rnd(hd), rnd(hd)
@@ -880,9 +882,6 @@ def relurax_bench(args) -> int:
             hd, page, 1e-5, torch.bfloat16), reps=8)
         record(f"vudivik_bias_norm_rope_cache_{label}", ms,
                nbytes=tokens * ((H + 2 * G) * hd * 4 + H * hd * 2 + 2 * G * hd * 2.0))
-        o = rnd(tokens, H * hd)
-        ms = _time_graph(lambda: ops.head_gate_mul(o, qkv[:, channels:], H), reps=8)
-        record(f"head_gate_{label}", ms, nbytes=tokens * (H * hd * 4.0 + H * 4))
         # the Llama decoder's attention on the same cache: every key (no window)
         out_l = torch.empty(tokens, H * hd, dtype=torch.bfloat16, device=dev)
         turn["i"] = 0

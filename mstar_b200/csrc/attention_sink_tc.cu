@@ -31,7 +31,14 @@ struct SinkTcArgs {
     float* scratch;
     int q_stride, bt_stride, nq, nkv, hd, vd, page_size, window, keep_first, splits;
     float scale_log2e;
+    // not null: the output of head h of token t is multiplied by sigmoid(gate[t * gate_stride + h])
+    const float* gate;
+    int gate_stride;
 };
+
+__device__ __forceinline__ float st_head_gate(const float* gate, int stride, int tok, int head) {
+    return gate == nullptr ? 1.f : 1.f / (1.f + expf(-gate[(size_t)tok * stride + head]));
+}
 
 template <int D> __device__ __forceinline__ int st_off(int row, int c) { return row * (D + 8) + c * 8; }
 
@@ -58,6 +65,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
     const unsigned long long waited = pdl_wait();
     const bf16* q = pdl_after(a.q, waited);
     const bf16* kv = pdl_after(a.kv, waited);
+    const float* gate = pdl_after(a.gate, waited);
     const int q_start = a.qo_indptr[e];
     const int q_len = a.qo_indptr[e + 1] - q_start;
     const int rows_total = q_len * G;
@@ -293,7 +301,9 @@ sink_attention_tc_kernel(SinkTcArgs a) {
             const int row = row0 + r;
             const int tok = q_start + row / G, head = kvh * G + row % G;
             if (a.splits == 1) {
-                if (d < a.vd) a.out[((size_t)tok * a.nq + head) * a.vd + d] = __float2bfloat16_rn(sum / L);
+                if (d < a.vd)
+                    a.out[((size_t)tok * a.nq + head) * a.vd + d] =
+                        __float2bfloat16_rn(sum / L * st_head_gate(gate, a.gate_stride, tok, head));
             } else {
                 float* dst = a.scratch + (((size_t)tok * a.nq + head) * a.splits + split) * pw;
                 dst[d] = d < a.vd ? sum : (d == a.vd ? M : L);
@@ -307,7 +317,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
         const float l = half ? l1 : l0, m = half ? m1 : m0;
         const int tok = q_start + row / G, head = kvh * G + row % G;
         if (a.splits == 1) {
-            const float inv = 1.f / l;
+            const float inv = st_head_gate(gate, a.gate_stride, tok, head) / l;
             bf16* dst = a.out + ((size_t)tok * a.nq + head) * a.vd + (lane & 3) * 2;
 #pragma unroll
             for (int n = 0; n < D / 8; ++n)
@@ -336,8 +346,11 @@ sink_attention_tc_kernel(SinkTcArgs a) {
 // round by shuffles, and every lane sums its features over the splits with the loads of all
 // splits in flight together.
 __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
-                                  int rows, int vd, int splits) {
-    scratch = pdl_after(scratch, pdl_wait());
+                                  int rows, int vd, int splits, const float* gate, int gate_stride,
+                                  int nq) {
+    const unsigned long long waited = pdl_wait();
+    scratch = pdl_after(scratch, waited);
+    gate = pdl_after(gate, waited);
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= rows) return;
     const float* base = scratch + (size_t)row * splits * (vd + 2);
@@ -352,7 +365,7 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
     }
     const float M = warp_max(fmaxf(m_a, m_b));
     const float w_a = exp2f(m_a - M), w_b = exp2f(m_b - M);   // 0 for a split that saw no key
-    const float L = warp_sum(l_a * w_a + l_b * w_b);
+    const float L = warp_sum(l_a * w_a + l_b * w_b) / st_head_gate(gate, gate_stride, row / nq, row % nq);
     for (int d0 = 0; d0 < vd; d0 += 32) {
         const int d = d0 + lane;
         float sum = 0.f;
@@ -397,14 +410,16 @@ static int launch_sink_tc(const SinkTcArgs& a, int entries, int max_q_len, cudaS
 }
 
 // Entries [0, entries) of the batch; q: [tokens] rows of q_stride elements; out: [tokens,
-// nq * vd]; scratch: float [tokens * nq * splits * (vd + 2)] when splits > 1.  Returns 0, a
+// nq * vd]; scratch: float [tokens * nq * splits * (vd + 2)] when splits > 1; gate: null, or
+// float rows of gate_stride with one number a head, whose sigmoid scales that head's output.
+// Returns 0, a
 // CUDA error code, or -1 when the shape is refused (sizes no multiples of 8 or above 256).
 MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, const void* kv_cache,
                                       const int* block_table, int bt_stride, const int* qo_indptr,
                                       const int* kv_len, int entries, int tokens, int max_q_len,
                                       int nq, int nkv, int hd, int vd, int page_size, int window,
                                       int keep_first, float scale, int splits, float* scratch,
-                                      void* stream) {
+                                      const float* gate, int gate_stride, void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || entries > 65535 || nkv > 65535) return -1;
     if (hd % 8 || vd % 8 || hd <= 0 || vd <= 0 || hd > 256 || vd > 256 || splits < 1 || splits > 64)
@@ -429,6 +444,8 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
     a.keep_first = window > 0 ? keep_first : 0;
     a.splits = splits;
     a.scale_log2e = scale * 1.4426950408889634f;
+    a.gate = gate;
+    a.gate_stride = gate_stride;
     cudaStream_t s = (cudaStream_t)stream;
     const int wide = hd > vd ? hd : vd;
     int code;
@@ -440,6 +457,6 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
     if (code != 0 || splits == 1) return code;
     const int rows = tokens * nq;
     mstar_launch(sink_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, (const float*)scratch,
-                 (bf16*)out, rows, vd, splits);
+                 (bf16*)out, rows, vd, splits, gate, gate_stride, nq);
     return launch_status();
 }

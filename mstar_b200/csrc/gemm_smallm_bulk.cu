@@ -78,8 +78,9 @@ struct SbRope {
     const float* inv_freq;   // [hd / 2]
     bf16* kv_cache;          // [pages, 2, nkv, page_size, hd]
     int nq, nkv, hd, page_size, bt_stride;
-    // plain form only: 1 squares the positive part of every sum before it is stored (a
-    // feed-forward's first product with its relu-squared, as one kernel)
+    // plain form: 1 squares the positive part of every sum before it is stored (a
+    // feed-forward's first product with its relu-squared, as one kernel); gated form: 0 gates
+    // by the SiLU, 2 by the tanh form of gelu
     int act;
 };
 
@@ -311,7 +312,10 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                     // gate and up are rounded to bfloat16 first, as the unfused path stores them
                     const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
                     const float up = __bfloat162float(__float2bfloat16_rn(v[STRIPS - 1]));
-                    y = gate / (1.f + expf(-gate)) * up;
+                    // act 2: the tanh form of gelu, 0.5 g (1 + tanh z) = g / (1 + exp(-2 z))
+                    const float z = rp.act == 2
+                        ? 1.5957691216057308f * (gate + 0.044715f * gate * gate * gate) : gate;
+                    y = gate / (1.f + expf(-z)) * up;
                 }
                 sb_store<OutT>(out + (size_t)m * ldo + n, y);
             }
@@ -381,8 +385,8 @@ static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out
     }
 }
 
-// out[M, N] = x W^T (gated == 0), or out[M, N/2] = silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu]
-// (gated == 1, N even, bfloat16 out).  x: [M, K] bf16 with row stride ldx, W: [N, K] bf16 with
+// out[M, N] = x W^T (gated == 0), or out[M, N/2] = act(x Wg^T) * (x Wu^T) for W = [Wg; Wu]
+// (gated == 1: act the SiLU, gated == 2: the tanh form of gelu; N even, bfloat16 out).  x: [M, K] bf16 with row stride ldx, W: [N, K] bf16 with
 // row stride ldw, out: bf16 or float (out_dtype) with row stride ldo.  Returns 0, a CUDA error
 // code, or -1 when the shape is refused: M outside 1..16, K no multiple of 32, leading
 // dimensions not multiples of 8 elements or pointers not 16-byte aligned (bulk copies), N odd
@@ -400,9 +404,10 @@ MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* ou
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
     if (gated) {
+        const int act = gated == 2 ? 2 : 0;
         if (M > 8)
-            return launch_bulk<true, true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s);
-        return launch_bulk<true, false, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s);
+            return launch_bulk<true, true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s, act);
+        return launch_bulk<true, false, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s, act);
     }
     if (out_dtype == MSTAR_F32) {
         if (M > 8) return launch_bulk<false, true, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);

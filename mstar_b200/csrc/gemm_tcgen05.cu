@@ -424,7 +424,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
 gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out, int M,
                                int N, int K, int ldo, int tiles_m, int tiles_total,
-                               int* __restrict__ error_word) {
+                               int* __restrict__ error_word, int gate_act) {
     static_assert(BN == 256 || BN == 192 || BN == 128, "pair tile width");
     static_assert(!GATED || BN == 256, "the gated form keeps gate and up in 128 columns each");
     constexpr int OUT_COLS = GATED ? BN / 2 : BN;
@@ -591,7 +591,10 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                     for (int i = 0; i < 32; ++i) {
                         const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
                         const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
-                        r[i] = __float_as_uint(g / (1.f + expf(-g)) * v);
+                        // gate_act 1: the tanh form of gelu, 0.5 g (1 + tanh z) = g / (1 + exp(-2 z))
+                        const float z = gate_act == 1
+                            ? 1.5957691216057308f * (g + 0.044715f * g * g * g) : g;
+                        r[i] = __float_as_uint(g / (1.f + expf(-z)) * v);
                     }
                     const int col = n0 + c0;
                     if (row < M && col < N)
@@ -612,7 +615,7 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
 
 template <int BN, int STAGES, bool GATED, typename OutT>
 static int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, int M, int N,
-                                int K, int ldo, int* error_word, cudaStream_t s) {
+                                int K, int ldo, int* error_word, cudaStream_t s, int gate_act = 0) {
     const size_t smem = (size_t)STAGES * (TC_BM + BN / 2) * TC_BK * 2 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -628,7 +631,7 @@ static int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, Ou
     const int on_gpu = pairs_on_gpu();
     const int pairs = total < on_gpu ? total : on_gpu;
     gemm_tcgen05_persistent_kernel<BN, STAGES, GATED, OutT><<<2 * pairs, TC_THREADS, smem, s>>>(
-        ma, mb, out, M, N, K, ldo, tiles_m, total, error_word);
+        ma, mb, out, M, N, K, ldo, tiles_m, total, error_word, gate_act);
     return launch_status();
 }
 
@@ -677,12 +680,13 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, in
 // when the shape is refused (K or a leading dimension not a multiple of 8 elements,
 // operands not 16-byte aligned, bn not 128 or 256), -3 / -4 when the tensor map cannot
 // be made.
-// out[M, N/2] = silu(x Wg^T) * (x Wu^T) for the fused W = [Wg; Wu] of N rows, bfloat16, on
-// pairs of CTAs.  Refusals and error word as mstar_gemm_tcgen05_bf16; N/2 must be a
-// multiple of 8.
+// out[M, N/2] = act(x Wg^T) * (x Wu^T) for the fused W = [Wg; Wu] of N rows, bfloat16, on
+// pairs of CTAs; gate_act 0: the SiLU, 1: the tanh form of gelu.  Refusals and error word as
+// mstar_gemm_tcgen05_bf16; N/2 must be a multiple of 8.
 MSTAR_API int mstar_gemm_tcgen05_gated_bf16(const void* x, const void* W, void* out, int M, int N,
                                             int K, int ldx, int ldw, int ldo, int* error_word,
-                                            void* stream) {
+                                            int gate_act, void* stream) {
+    if (gate_act != 0 && gate_act != 1) return -1;
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || N % 16 != 0) return -1;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -1;
@@ -692,7 +696,7 @@ MSTAR_API int mstar_gemm_tcgen05_gated_bf16(const void* x, const void* W, void* 
     rc = make_map(&mb, W, N, K, ldw, 128);
     if (rc != 0) return rc;
     return launch_tc_persistent<256, 6, true, bf16>(ma, mb, (bf16*)out, M, N / 2, K, ldo, error_word,
-                                                    (cudaStream_t)stream);
+                                                    (cudaStream_t)stream, gate_act);
 }
 
 MSTAR_API int mstar_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int M, int N, int K,

@@ -395,8 +395,10 @@ def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool,
+def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated,
                  static_weights: bool = False):
+    """``gated``: False or 0 for the plain product; True or 1 gates by the SiLU, 2 by the tanh
+    form of gelu."""
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
@@ -564,9 +566,11 @@ def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None
     return out
 
 
-def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor):
-    """silu(x Wg^T) * (x Wu^T) for the fused [Wg; Wu] on pairs of CTAs (cta_group::2),
-    the activation applied in the epilogue straight from tensor memory."""
+def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor, kind: str = "silu"):
+    """act(x Wg^T) * (x Wu^T) for the fused [Wg; Wu] on pairs of CTAs (cta_group::2), the
+    activation (``kind``: "silu" or "gelu_tanh") applied in the epilogue straight from tensor
+    memory."""
+    assert kind in ("silu", "gelu_tanh")
     _need_cuda(x, w_gate_up)
     assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
     assert x.stride(1) == 1 and w_gate_up.stride(1) == 1 and x.shape[1] == w_gate_up.shape[1]
@@ -575,7 +579,8 @@ def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor):
     out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
     code = lib.get("gemm_tcgen05").mstar_gemm_tcgen05_gated_bf16(
         x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), m, n, k, x.stride(0),
-        w_gate_up.stride(0), out.stride(0), tcgen05_error_word(x.device).data_ptr(), _stream())
+        w_gate_up.stride(0), out.stride(0), tcgen05_error_word(x.device).data_ptr(),
+        0 if kind == "silu" else 1, _stream())
     if code == -1:
         raise KernelError(f"gated tcgen05 GEMM refuses M={m}, N={n}, K={k}")
     if code in (-3, -4):
@@ -673,16 +678,17 @@ def linear_act(x: torch.Tensor, w: torch.Tensor, kind: str, static_weights: bool
 def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = False,
              kind: str = "silu"):
     """act(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu], act the SiLU or (``kind``
-    "gelu_tanh") the tanh form of gelu: one kernel for few bfloat16 rows, else the product
+    "gelu_tanh") the tanh form of gelu: one kernel for bfloat16 rows whose shapes the small-M
+    or the tcgen05 kernel takes (MSTAR_FUSED_ACT=0: never for the gelu), else the product
     followed by the activation-multiply kernel."""
     _need_cuda(x, w_gate_up)
-    if kind == "silu":
+    if kind == "silu" or (kind == "gelu_tanh" and os.environ.get("MSTAR_FUSED_ACT") != "0"):
         if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
-            return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True,
+            return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=1 if kind == "silu" else 2,
                                 static_weights=static_weights)
         if (_tc_ok(x, w_gate_up) and w_gate_up.shape[0] % 16 == 0
                 and tcgen05_tile(x.shape[0], w_gate_up.shape[0]) is not None):
-            return gemm_tcgen05_gated(x, w_gate_up)
+            return gemm_tcgen05_gated(x, w_gate_up, kind)
     return silu_mul(linear(x, w_gate_up, static_weights=static_weights), kind=kind)
 
 
@@ -1040,6 +1046,9 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tens
     return out
 
 
+_BMM_INTO_ROWS: dict = {}       # out dtype -> False once the library refused the strided output
+
+
 def linear_per_head(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
     """out[t, h, :] = x[t, h, :] @ w[h]^T for x [tokens, heads, K] (any token and head strides,
     last stride 1) and w [heads, N, K].  bfloat16: the library's batched GEMM; float32: this
@@ -1051,6 +1060,18 @@ def linear_per_head(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | N
     out_dtype = out_dtype or x.dtype
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         a, b = x.transpose(0, 1), w.transpose(1, 2)
+        # the library writes [heads, tokens, n] straight into the rows of [tokens, heads, n]
+        # (a row stride of heads * n), so no copy follows the product
+        out = torch.empty((tokens, heads, n), dtype=out_dtype, device=x.device)
+        if _BMM_INTO_ROWS.get(out_dtype, True):
+            try:
+                if out_dtype == torch.float32:
+                    torch.bmm(a, b, out_dtype=torch.float32, out=out.transpose(0, 1))
+                else:
+                    torch.bmm(a, b, out=out.transpose(0, 1))
+                return out
+            except (TypeError, RuntimeError):
+                _BMM_INTO_ROWS[out_dtype] = False
         if out_dtype == torch.float32:
             try:
                 return torch.bmm(a, b, out_dtype=torch.float32).transpose(0, 1).contiguous()
@@ -1271,16 +1292,21 @@ def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_h
 
 def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_req, cache_pos,
                    num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, page_size: int,
-                   window: int, keep_first: int, scale: float, ctx=None) -> torch.Tensor:
+                   window: int, keep_first: int, scale: float, ctx=None, gate=None) -> torch.Tensor:
     """Softmax attention of every token over the keys it sees: those of the last ``window``
     positions (0: all) and the first ``keep_first`` of the sequence.  ``q``: [tokens, heads *
-    head_dim]; returns [tokens, heads * v_dim].  bfloat16 with sizes that are multiples of 8
+    head_dim]; returns [tokens, heads * v_dim].  ``gate``: None, or float [tokens, heads] (a
+    column view of a wider product): head h's output is multiplied by sigmoid(gate[t, h]),
+    where the tensor-core kernel writes it out, by a kernel of its own after the other.  bfloat16 with sizes that are multiples of 8
     up to 256 and a step context (``ctx``: entries, their token ranges and lengths) runs on
     the tensor cores (MSTAR_SINK_ATTENTION=generic: never); everything else, float32
     included, on the CUDA cores."""
-    _need_cuda(q, kv_cache, block_table, token_req, cache_pos)
+    _need_cuda(q, kv_cache, block_table, token_req, cache_pos, gate)
     assert q.is_contiguous() and kv_cache.is_contiguous() and kv_cache.dtype == q.dtype
     tokens = q.shape[0]
+    if gate is not None:
+        assert tuple(gate.shape) == (tokens, num_heads) and gate.stride(1) == 1
+        assert gate.dtype == torch.float32
     out = torch.empty((tokens, num_heads * v_dim), dtype=q.dtype, device=q.device)
     if (ctx is not None and q.dtype == torch.bfloat16 and head_dim % 8 == 0 and v_dim % 8 == 0
             and max(head_dim, v_dim) <= 256 and os.environ.get("MSTAR_SINK_ATTENTION") != "generic"):
@@ -1298,7 +1324,7 @@ def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_r
             block_table.stride(0), ctx.qo_indptr.data_ptr(), ctx.kv_len.data_ptr(),
             ctx.num_entries, tokens, ctx.max_q_len, num_heads, num_kv_heads, head_dim, v_dim,
             page_size, int(window or 0), int(keep_first), float(scale), splits, _ptr(scratch),
-            _stream())
+            _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
         if code == -1:
             raise KernelError(f"tensor-core window attention refuses heads={num_heads}, "
                               f"kv_heads={num_kv_heads}, head_dim={head_dim}, v_dim={v_dim}")
@@ -1315,6 +1341,8 @@ def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_r
         raise KernelError(f"window attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
                           f"head_dim={head_dim}, v_dim={v_dim}")
     check(code, "sink_attention")
+    if gate is not None:
+        head_gate_mul(out, gate, num_heads)
     return out
 
 

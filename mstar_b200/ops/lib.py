@@ -65,7 +65,7 @@ _SIGNATURES = {
     },
     "attention_sink_tc": {
         "mstar_sink_attention_tc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                    _i, _i, _i, _i, _f, _i, _vp, _vp],
+                                    _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp],
     },
     "selective_scan": {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,
@@ -104,7 +104,7 @@ _SIGNATURES = {
     },
     "gemm_tcgen05": {
         "mstar_gemm_tcgen05_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
-        "mstar_gemm_tcgen05_gated_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
+        "mstar_gemm_tcgen05_gated_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _i, _vp],
     },
     "gemm_skinny": {
         "mstar_gemm_skinny_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],

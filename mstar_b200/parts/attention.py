@@ -144,13 +144,11 @@ class Attention:
         if s.conv_taps > 1:
             ops.conv_state_advance(qkv, (s.num_heads + s.num_kv_heads) * s.head_dim, s.conv_taps,
                                    ctx.qo_indptr, ctx.slots, cache.state, ctx.num_entries)
+        gate = qkv[:, qkv.shape[1] - s.num_heads:] if s.head_gate else None
         out = ops.sink_attention(q, cache.kv, cache.block_table, ctx.token_req, ctx.cache_pos,
                                  s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
                                  cache.page_size, s.window or 0, s.keep_first if s.window else 0,
-                                 self.scale, ctx=ctx)
-        if s.head_gate:
-            gate_at = qkv.shape[1] - s.num_heads
-            ops.head_gate_mul(out, qkv[:, gate_at:], s.num_heads)
+                                 self.scale, ctx=ctx, gate=gate)
         return ops.linear(out, self.w_out, static_weights=True)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:
