@@ -40,6 +40,13 @@ __device__ __forceinline__ float conv_feature(const float* __restrict__ row, con
                                               int channels, int i, const PrepArgs& a) {
     float y = 0.f;
     const int keep = a.taps - 1;
+    if (keep <= i) {                                     // every row is of this portion
+        const float* u = row - (ptrdiff_t)keep * a.row_stride + col;
+        const W* wc = w + (size_t)chan * a.taps;
+#pragma unroll 4
+        for (int j = 0; j < a.taps; ++j) y = fmaf(to_float(wc[j]), u[(ptrdiff_t)j * a.row_stride], y);
+        return y;
+    }
     for (int j = 0; j < a.taps; ++j) {
         const int back = keep - j;                       // rows before this token
         const float u = back <= i ? *(row - (ptrdiff_t)back * a.row_stride + col)
@@ -97,7 +104,8 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
     A* page_base = kv_cache + (size_t)page * page_elems;
     float* mine = heads + warp * a.hd;
     const int nheads = a.v_from_k ? a.nq + a.nkv : a.nq + 2 * a.nkv;
-    for (int h = warp; h < nheads; h += nwarps) {
+    // few tokens (decoding): the heads of a token are dealt out among gridDim.y blocks
+    for (int h = blockIdx.y * nwarps + warp; h < nheads; h += nwarps * gridDim.y) {
         if (h >= a.nq + a.nkv) {               // a value head: bias, then the page
             const int g = h - a.nq - a.nkv;
             const int off = (a.nq + a.nkv) * a.hd + g * a.vd;
@@ -175,8 +183,18 @@ MSTAR_API int mstar_sink_prepare(const float* qkv, const void* bias, const void*
     PrepArgs a{nq, nkv, hd, vd, rot, page_size, bt_stride, nq * hd, eps, norm, row_stride, taps,
                v_from_k, state_stride};
     cudaStream_t s = (cudaStream_t)stream;
+    // a block takes 8 heads at a time: with fewer blocks than SMs, a token's heads go to
+    // several blocks (each makes the token's sines and cosines for itself)
+    const int nheads = v_from_k ? nq + nkv : nq + 2 * nkv;
+    int head_blocks = 1;
+    if (tokens < device_sm_count()) {
+        head_blocks = (nheads + threads / 32 - 1) / (threads / 32);
+        const int room = (2 * device_sm_count() + tokens - 1) / tokens;
+        if (head_blocks > room) head_blocks = room;
+        if (head_blocks < 1) head_blocks = 1;
+    }
 #define GO(A, W)                                                                                  \
-    mstar_launch((sink_prepare_kernel<A, W>), dim3(tokens), dim3(threads), smem, s, qkv,          \
+    mstar_launch((sink_prepare_kernel<A, W>), dim3(tokens, head_blocks), dim3(threads), smem, s, qkv, \
                  (const W*)bias, (const W*)q_norm, (const W*)k_norm, freq, positions, cache_pos,  \
                  token_req, block_table, (A*)q_out, (A*)kv_cache, (const W*)conv_q,               \
                  (const W*)conv_k, qo_indptr, slots, state, a)

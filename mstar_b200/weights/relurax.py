@@ -22,6 +22,7 @@ from .tifosun import _stack
 
 def relurax_checkpoint_map(config, layout: ModelLayout) -> CheckpointMap:
     src: list = []
+    unused: set = set()     # norms of a second sublayer that a layer without a feed-forward lacks
     width = layout.hidden_size
     src.append(TensorSource("embed", "embed.weight", 0, layout.vocab_size))
     for i, block in enumerate(layout.blocks):
@@ -62,6 +63,7 @@ def relurax_checkpoint_map(config, layout: ModelLayout) -> CheckpointMap:
             raise ValueError(f"no checkpoint names for a mixer of kind {m.kind!r}")
         f = block.ffn
         if f is None:
+            unused.update((f"{ck}.norm2", f"{ck}.norm2b"))      # present or not: never read
             continue
         if f.kind == "gated_mlp":
             _stack(src, f"{me}.ffn.gate_up.weight", [(f"{ck}.mlp.gate", f.intermediate_size),
@@ -71,4 +73,4 @@ def relurax_checkpoint_map(config, layout: ModelLayout) -> CheckpointMap:
             raise ValueError(f"no checkpoint names for a feed-forward of kind {f.kind!r}")
     src.append(TensorSource("final.norm", "final_norm.weight", 0, layout.final_norm.size))
     src.append(TensorSource("head", "head.weight", 0, layout.vocab_size))
-    return CheckpointMap(sources=src)
+    return CheckpointMap(sources=src, ignore=unused.__contains__)

@@ -133,3 +133,12 @@ def test_plain_model_is_the_same_whole_and_in_parts():
     other = dict(w)
     other["l1.mix.dkv"] = w["l1.mix.dkv"][::-1].copy()
     assert np.abs(P.PlainRelurax(U.MIXED, other).forward(toks)[0] - whole).max() > 1e-3
+
+
+def test_norms_of_an_absent_feed_forward_are_not_read():
+    """A checkpoint may carry norm2 / norm2b for a layer without a feed-forward; the map
+    leaves them alone, and still names any other tensor it has no place for."""
+    lay = config_from_dict(U.MIXED).layout()
+    cmap = get_architecture("Relurax").checkpoint_map(config_from_dict(U.MIXED), lay)
+    assert cmap.ignore("l2.norm2") and cmap.ignore("l2.norm2b")
+    assert not cmap.ignore("l0.norm2") and not cmap.ignore("l2.norm1") and not cmap.ignore("l2.mlp.up")
