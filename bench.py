@@ -489,7 +489,7 @@ def arch_bench(args) -> int:
             c = caches[turn["i"] % copies]
             turn["i"] += 1
             return ops.latent_attention(q_abs, q_rot, c, table, token_req, cache_pos, heads, rank,
-                                        rot, page, window, att["scale"])
+                                        rot, page, window, att["scale"], entries=reqs)
 
         ms = _time_graph(attend, reps=max(copies, 4) if label == "decode" else 2)
         keys = sum(min(ctx - per + k + 1, window) for k in range(per)) * reqs
@@ -917,7 +917,8 @@ def relurax_bench(args) -> int:
             c = caches[turn["i"] % copies]
             turn["i"] += 1
             return ops.latent_attention(q_abs, q_rot, c, table, token_req, cache_pos, heads, rank,
-                                        rot, page, win, lat["scale"], max_keys=ctx_len)
+                                        rot, page, win, lat["scale"], max_keys=ctx_len,
+                                        entries=reqs)
 
         reps = max(copies, 4) if label == "decode" else 2
         for name, win in (("latent_attention", 0), ("tifosun_latent_attention_window_512", 512)):
@@ -1144,7 +1145,7 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool, cfg: dict) -> int
             q_rot = rnd(batch * per, heads, rot)
             fn = lambda: ops.latent_attention(q_abs, q_rot, cache, table, token_req, cache_pos, heads,
                                               rank, rot, PAGE_SIZE, window, m["scale"],
-                                              max_keys=length)
+                                              max_keys=length, entries=batch)
             ms = _time_graph(fn, reps=4)
             keys = sum(min(length - per + k + 1, window) for k in range(per)) * batch
             flops = 2.0 * heads * keys * (2 * rank + rot)

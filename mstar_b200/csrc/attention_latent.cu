@@ -33,6 +33,9 @@ struct LatentArgs {
     int q_head;   // elements between heads of the rotated query part
     int splits;   // blocks that share a token's keys (tile i goes to block i % splits)
     float scale;
+    int row_heads = 0;   // rows a token takes in a block of several tokens (a power of two)
+    int num_tokens = 0;
+    int cols = 0;        // output columns a block of several tokens makes
 };
 
 // A row of D cache elements into floats in shared memory; 16-byte loads where the row allows.
@@ -578,6 +581,249 @@ latent_attention_tc_kernel(const float* __restrict__ q_abs, const bf16* __restri
     }
 }
 
+// The same arithmetic for prompts: a block takes several tokens that follow one another in the
+// step, 64 rows of (token, head), a token's heads padded to `row_heads` rows, so that a tile of
+// keys is fetched once for all of them and no row of a product tile is empty.  Warp w owns rows
+// 16w .. 16w+15 from the scores to the output: its scores of a tile's 32 keys stay in the
+// accumulator registers, the softmax runs there (a row's keys lie in the four lanes of a quad),
+// and the probabilities go into the second product as its A fragments, again in three bfloat16
+// parts, so nothing but the queries and the keys passes through shared memory and a round has
+// two barriers (around the tile's copy).  Every row masks by its own token's position
+// (lo <= key < hi).  Tokens of one request share a block table; where a block's tokens belong
+// to several requests it walks them request by request, the other rows idle.  A block makes
+// `cols` of the output's columns (blockIdx.z: a wide latent is shared among two blocks, each
+// scoring for itself).  Keys are never shared among blocks here.
+__device__ __forceinline__ uint32_t pack_bf16(bf16 lo, bf16 hi) {
+    return (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+}
+
+template <int NBT>
+__global__ void __launch_bounds__(128, 1)
+latent_attention_rows_kernel(const float* __restrict__ q_abs, const bf16* __restrict__ q_rot,
+                             float* __restrict__ out, const bf16* __restrict__ cache,
+                             const int* __restrict__ block_table, const int* __restrict__ token_req,
+                             const int* __restrict__ cache_pos, LatentArgs a) {
+    constexpr int ROWS = 64, THREADS = 128;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int GP = a.row_heads, TPB = ROWS / GP;
+    const int t0 = blockIdx.x * TPB, h0 = blockIdx.y * a.group;
+    const int G = min(a.group, a.heads - h0);
+    const int ntok = min(TPB, a.num_tokens - t0);
+    const int D = a.rank + a.rot, DP = D + 8;
+    const int col0 = blockIdx.z * a.cols;
+    const int nb_cols = min(a.cols, a.rank - col0) >> 3;     // tiles of 8 columns, an even count
+    bf16* qh = reinterpret_cast<bf16*>(smem_raw);      // [ROWS][DP] head of the query
+    bf16* ql = qh + ROWS * DP;                         // [ROWS][DP] remainder
+    bf16* tile = ql + ROWS * DP;                       // [TILE][DP]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const unsigned long long waited = pdl_wait();
+    q_abs = pdl_after(q_abs, waited);
+    q_rot = pdl_after(q_rot, waited);
+    cache = pdl_after(cache, waited);
+
+    for (int i = tid; i < ROWS * D; i += THREADS) {
+        const int r = i / D, d = i - r * D;
+        const int tk = r / GP, hd = r - tk * GP;
+        float v = 0.f;
+        if (tk < ntok && hd < G) {
+            const size_t t = (size_t)(t0 + tk);
+            v = d < a.rank ? q_abs[(t * a.heads + h0 + hd) * a.rank + d]
+                           : to_float(q_rot[t * a.ldq + (size_t)(h0 + hd) * a.q_head + (d - a.rank)]);
+        }
+        const bf16 head = __float2bfloat16_rn(v);
+        qh[r * DP + d] = head;
+        ql[r * DP + d] = __float2bfloat16_rn(v - __bfloat162float(head));
+    }
+    const int chunks = D >> 3;
+    const int g = lane >> 2, t4 = lane & 3;
+    int row_tk[2], row_hd[2];                          // this thread's rows: 16 warp + g, + 8
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = warp * 16 + g + 8 * i;
+        row_tk[i] = r / GP;
+        row_hd[i] = r - row_tk[i] * GP;
+    }
+    float acc[NBT][4];
+
+    for (int s0 = 0; s0 < ntok;) {
+        // tokens s0 .. s1-1 of the block belong to one request
+        const int req = token_req[t0 + s0];
+        int s1 = s0 + 1;
+        while (s1 < ntok && token_req[t0 + s1] == req) ++s1;
+        int lo_min = 0x7fffffff, hi_max = 0;
+        for (int tk = s0; tk < s1; ++tk) {
+            const int hi = cache_pos[t0 + tk] + 1;
+            const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+            lo_min = min(lo_min, lo);
+            hi_max = max(hi_max, hi);
+        }
+        const int* bt = block_table + (size_t)req * a.bt_stride;
+        int lo_r[2], hi_r[2];                          // hi 0: an idle row
+        int warp_lo = 0x7fffffff, warp_hi = 0;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            lo_r[i] = hi_r[i] = 0;
+            if (row_tk[i] >= s0 && row_tk[i] < s1 && row_hd[i] < G) {
+                hi_r[i] = cache_pos[t0 + row_tk[i]] + 1;
+                lo_r[i] = (a.window > 0 && hi_r[i] > a.window) ? hi_r[i] - a.window : 0;
+                warp_lo = min(warp_lo, lo_r[i]);
+                warp_hi = max(warp_hi, hi_r[i]);
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            warp_lo = min(warp_lo, __shfl_xor_sync(0xffffffffu, warp_lo, o));
+            warp_hi = max(warp_hi, __shfl_xor_sync(0xffffffffu, warp_hi, o));
+        }
+        float m_r[2] = {-INFINITY, -INFINITY}, l_r[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nb = 0; nb < NBT; ++nb)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[nb][i] = 0.f;
+
+        for (int base = lo_min; base < hi_max; base += LAT_TILE) {
+            __syncthreads();                           // the tile of the round before is done with
+            for (int j = warp; j < LAT_TILE; j += THREADS / 32) {
+                const int key = base + j;
+                const bool seen = key < hi_max;
+                const bf16* src = cache;
+                if (seen) src = cache + ((size_t)bt[key / a.page_size] * a.page_size + key % a.page_size) * D;
+                for (int c = lane; c < chunks; c += 32)
+                    cp_async_16(smem_u32(tile + j * DP + c * 8), seen ? src + c * 8 : cache, seen ? 16 : 0);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+            __syncthreads();
+            if (base >= warp_hi || base + LAT_TILE <= warp_lo) continue;   // nothing for these rows
+            // scores of the warp's 16 rows and the tile's 32 keys: four tiles of 8 keys
+            // (the head and the remainder of the query in chains of their own, so that a
+            // product does not wait for the one before it)
+            float sc[4][4], sr[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) sc[j][i] = sr[j][i] = 0.f;
+            {
+                const int arow = warp * 16 + (lane & 15), acol = (lane >> 4) * 8;
+                const int krow = (lane & 7) + ((lane >> 4) << 3), kcol = ((lane >> 3) & 1) * 8;
+                const uint32_t qh_at = smem_u32(qh + arow * DP + acol), ql_at = smem_u32(ql + arow * DP + acol);
+                const uint32_t k_at = smem_u32(tile + krow * DP + kcol);
+                for (int k0 = 0; k0 < D; k0 += 16) {
+                    uint32_t ah[4], al[4], k01[4], k23[4];
+                    ldmatrix_x4(ah, qh_at + 2 * k0);
+                    ldmatrix_x4(al, ql_at + 2 * k0);
+                    ldmatrix_x4(k01, k_at + 2 * k0);
+                    ldmatrix_x4(k23, k_at + 2 * (16 * DP + k0));
+                    mma_bf16_16816(sc[0], ah, k01[0], k01[1]);
+                    mma_bf16_16816(sc[1], ah, k01[2], k01[3]);
+                    mma_bf16_16816(sc[2], ah, k23[0], k23[1]);
+                    mma_bf16_16816(sc[3], ah, k23[2], k23[3]);
+                    mma_bf16_16816(sr[0], al, k01[0], k01[1]);
+                    mma_bf16_16816(sr[1], al, k01[2], k01[3]);
+                    mma_bf16_16816(sr[2], al, k23[0], k23[1]);
+                    mma_bf16_16816(sr[3], al, k23[2], k23[3]);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) sc[j][i] += sr[j][i];
+            }
+            // mask, softmax of the tile in registers: row i of the thread has its keys in
+            // sc[j][2 i], sc[j][2 i + 1] (keys base + 8 j + 2 t4, + 1) of the quad's four lanes
+            uint32_t pa[2][3][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float mx = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int key = base + 8 * j + 2 * t4 + c;
+                        const float v = (key >= lo_r[i] && key < hi_r[i]) ? sc[j][2 * i + c] * a.scale
+                                                                         : -INFINITY;
+                        sc[j][2 * i + c] = v;
+                        mx = fmaxf(mx, v);
+                    }
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float m_new = fmaxf(m_r[i], mx);
+                const bool none = m_new == -INFINITY;  // the row has seen no key yet
+                const float m_use = none ? 0.f : m_new;
+                const float alpha = none ? 1.f : expf(m_r[i] - m_new);
+                m_r[i] = m_new;
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    bf16 part[3][2];
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const float p = expf(sc[j][2 * i + c] - m_use);
+                        sum += p;
+                        part[0][c] = __float2bfloat16_rn(p);
+                        const float r1 = p - __bfloat162float(part[0][c]);
+                        part[1][c] = __float2bfloat16_rn(r1);
+                        part[2][c] = __float2bfloat16_rn(r1 - __bfloat162float(part[1][c]));
+                    }
+                    // A fragment of the k-step j / 2: register i (+ 2 for the upper 8 keys)
+#pragma unroll
+                    for (int q = 0; q < 3; ++q) pa[j >> 1][q][i + 2 * (j & 1)] = pack_bf16(part[q][0], part[q][1]);
+                }
+                l_r[i] = l_r[i] * alpha + sum;
+#pragma unroll
+                for (int nb = 0; nb < NBT; ++nb) {
+                    acc[nb][2 * i] *= alpha;
+                    acc[nb][2 * i + 1] *= alpha;
+                }
+            }
+            // weighted sum: acc += P V over the block's columns
+            {
+                const int vrow = (lane & 7) + ((lane >> 3) & 1) * 8, vcol = (lane >> 4) * 8;
+#pragma unroll
+                for (int kk = 0; kk < 2; ++kk) {
+                    // two pairs of column tiles at a time: four sums take the three parts in
+                    // turn, so that a product does not wait for the one before it
+#pragma unroll
+                    for (int nb = 0; nb < NBT; nb += 4) {
+                        if (nb < nb_cols) {
+                            uint32_t v[4], w[4];
+                            const bool two = nb + 2 < nb_cols;
+                            const uint32_t at = smem_u32(tile + (16 * kk + vrow) * DP + col0 + nb * 8 + vcol);
+                            ldmatrix_x4_trans(v, at);
+                            ldmatrix_x4_trans(w, two ? at + 32 : at);
+#pragma unroll
+                            for (int q = 2; q >= 0; --q) {
+                                mma_bf16_16816(acc[nb], pa[kk][q], v[0], v[1]);
+                                mma_bf16_16816(acc[nb + 1], pa[kk][q], v[2], v[3]);
+                                if (two) {
+                                    mma_bf16_16816(acc[nb + 2], pa[kk][q], w[0], w[1]);
+                                    mma_bf16_16816(acc[nb + 3], pa[kk][q], w[2], w[3]);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float l = l_r[i];
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            if (hi_r[i] == 0) continue;
+            const float inv = 1.f / l;
+            const size_t th = (size_t)(t0 + row_tk[i]) * a.heads + h0 + row_hd[i];
+            float* dst = out + th * a.rank + col0 + 2 * t4;
+#pragma unroll
+            for (int nb = 0; nb < NBT; ++nb)
+                if (nb < nb_cols)
+                    *reinterpret_cast<float2*>(dst + nb * 8) =
+                        make_float2(acc[nb][2 * i] * inv, acc[nb][2 * i + 1] * inv);
+        }
+        s0 = s1;
+    }
+}
+
 // out[t, h, :] = sum_s exp(m_s - M) acc_s / sum_s exp(m_s - M) l_s, in the order of the splits.
 // A split that saw no key has l = 0 and m = -inf and adds nothing.
 __global__ void latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
@@ -636,7 +882,7 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
                                      int bt_stride, const int* token_req, const int* cache_pos,
                                      int num_tokens, int heads, int rank, int rot, int page_size,
                                      int window, float scale, int act_dtype, int group, int splits,
-                                     float* scratch, void* stream) {
+                                     float* scratch, int portions, void* stream) {
     if (num_tokens <= 0) return 0;
     if (heads <= 0 || rank <= 0 || rot < 0 || rank > 8 * LAT_THREADS) return -1;
     // heads a block: a thread has 32 sums for GP heads x (rank / 128) columns
@@ -670,6 +916,50 @@ MSTAR_API int mstar_latent_attention(const float* q_abs, const void* q_rot, int 
     if (scores_only < 0) {
         const char* e = getenv("MSTAR_LATENT_ATTENTION");
         scores_only = (e != nullptr && e[0] == 's') ? 1 : 0;
+    }
+    // `portions`: the step's tokens come in runs of one request (prompt portions), so a block
+    // takes the rows of several tokens (MSTAR_LATENT_ATTENTION=token keeps a token a block)
+    static int token_only = -1;
+    if (token_only < 0) {
+        const char* e = getenv("MSTAR_LATENT_ATTENTION");
+        token_only = (e != nullptr && e[0] == 't') ? 1 : 0;
+    }
+    if (portions && splits == 1 && act_dtype == MSTAR_BF16 && D % 16 == 0 && rank % 32 == 0 &&
+        rank <= 256 && ((uintptr_t)cache & 15) == 0 && ((uintptr_t)out & 7) == 0 && !cores_only &&
+        !scores_only && !token_only) {
+        constexpr int ROWS = 64;
+        const int tc_group = heads < 16 ? heads : 16;
+        int row_heads = 1;
+        while (row_heads < tc_group) row_heads *= 2;
+        LatentArgs b = a;
+        b.group = tc_group;
+        b.row_heads = row_heads;
+        b.num_tokens = num_tokens;
+        // a block makes all of a row's columns: sharing them among blocks (each scoring for
+        // itself) cost more than the warps it added brought, at every rank tried
+        const int shares = 1;
+        b.cols = rank / shares;                        // a multiple of 16
+        const int per_block = ROWS / row_heads;
+        dim3 rows_grid((num_tokens + per_block - 1) / per_block, (heads + tc_group - 1) / tc_group,
+                       shares);
+        const size_t smem_rows = sizeof(bf16) * (size_t)(2 * ROWS + LAT_TILE) * (D + 8);
+        if (smem_rows <= 200 * 1024) {
+#define GO_ROWS(NBT)                                                                              \
+    {                                                                                             \
+        static size_t configured = 0;                                                             \
+        if (smem_rows > 48 * 1024 && smem_rows > configured) {                                    \
+            cudaFuncSetAttribute(latent_attention_rows_kernel<NBT>,                               \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_rows);    \
+            configured = smem_rows;                                                               \
+        }                                                                                         \
+        mstar_launch((latent_attention_rows_kernel<NBT>), rows_grid, dim3(128), smem_rows, s,     \
+                     q_abs, (const bf16*)q_rot, out, (const bf16*)cache, block_table, token_req,  \
+                     cache_pos, b);                                                               \
+    }
+            if (b.cols <= 64) GO_ROWS(8) else if (b.cols <= 128) GO_ROWS(16) else GO_ROWS(32)
+#undef GO_ROWS
+            return launch_status();
+        }
     }
     const size_t smem_tc = sizeof(bf16) * ((size_t)(32 + LAT_TILE) * (D + 8) + 3 * 16 * (LAT_TILE + 8)) +
                            sizeof(float) * (LAT_TILE * 16 + 3 * 16);

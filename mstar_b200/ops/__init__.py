@@ -1009,13 +1009,16 @@ def latent_attention_plan(tokens: int, heads: int, rank: int, max_keys: int,
 
 def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tensor, block_table,
                      token_req, cache_pos, heads: int, rank: int, rot: int, page_size: int,
-                     window: int, scale: float, max_keys: int | None = None) -> torch.Tensor:
+                     window: int, scale: float, max_keys: int | None = None,
+                     entries: int | None = None) -> torch.Tensor:
     """Softmax attention of every token over the latent rows it sees.  ``q_abs``: float
     [tokens, heads, rank], the plain query part with the key up-projection folded in;
     ``q_rot``: [tokens, heads, rot] view (last stride 1) of rotated query parts.  Returns the
     float [tokens, heads, rank] probability-weighted sums of latents.  ``max_keys`` bounds the
     keys any token sees (default: the window, or one tile when there is none); it only decides
-    among how many blocks a token's keys are shared."""
+    among how many blocks a token's keys are shared.  ``entries``: how many requests the
+    step's tokens belong to; where they come in runs of one request (four tokens an entry or
+    more) and no token's keys are shared among blocks, a block takes several tokens."""
     _need_cuda(q_abs, q_rot, cache, block_table, token_req, cache_pos)
     assert q_abs.dtype == torch.float32 and q_abs.is_contiguous()
     tokens = q_abs.shape[0]
@@ -1036,7 +1039,8 @@ def latent_attention(q_abs: torch.Tensor, q_rot: torch.Tensor, cache: torch.Tens
         q_abs.data_ptr(), q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1), out.data_ptr(),
         cache.data_ptr(), block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(),
         cache_pos.data_ptr(), tokens, heads, rank, rot, page_size, int(window or 0), float(scale),
-        _dt(cache), group, splits, _ptr(scratch), _stream())
+        _dt(cache), group, splits, _ptr(scratch),
+        int(entries is not None and tokens >= 4 * max(entries, 1)), _stream())
     if code == -1:
         raise KernelError(f"latent attention refuses rank={rank}, rot={rot} (rank at most 1024, "
                           "a tile of 32 rows within 200 KB of shared memory)")

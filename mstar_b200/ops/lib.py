@@ -44,7 +44,7 @@ _SIGNATURES = {
     },
     "attention_latent": {
         "mstar_latent_attention": [_vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
-                                   _i, _i, _f, _i, _i, _i, _vp, _vp],
+                                   _i, _i, _f, _i, _i, _i, _vp, _i, _vp],
         "mstar_latent_fill": [_vp, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp,
                               _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _f, _vp],
     },

@@ -120,7 +120,7 @@ class LatentAttention:
         lat = ops.latent_attention(q_abs, q[:, :, s.qk_dim:], cache.kv, cache.block_table,
                                    ctx.token_req, ctx.cache_pos, h, s.kv_rank, s.rot_dim,
                                    cache.page_size, s.window or 0, self.scale,
-                                   max_keys=ctx.max_kv_len)
+                                   max_keys=ctx.max_kv_len, entries=ctx.num_entries)
         if s.gated and s.gate_per_head:
             # one gate a head commutes with the head's value up-projection
             lat = ops.head_gate_mul(lat.view(-1, h * s.kv_rank), gate, h,

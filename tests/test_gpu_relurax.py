@@ -374,6 +374,65 @@ def test_a_layer_reads_the_rows_another_layer_cached(dtype):
     close(torch.cat(got1), want1, dtype, "the layer that reads", bf16=6e-2)
 
 
+@pytest.mark.parametrize("heads,rank,rot,window", [(8, 64, 16, 0), (3, 256, 32, 0), (16, 320, 64, 0),
+                                                    (20, 128, 16, 0), (5, 96, 32, 70), (1, 32, 16, 33),
+                                                    (16, 512, 64, 0), (2, 192, 0, 300)])
+def test_long_portions_share_key_tiles_among_tokens(heads, rank, rot, window):
+    """The latent attention kernel alone on a step of long and short portions of several
+    requests (the form where a block takes the rows of several tokens, portions ending inside
+    a block) against float64 sums: every key before the token, or a window; one token of each
+    long portion has a score that stands out on a key far back, or just outside the window."""
+    from mstar_b200 import ops
+
+    page, D = 16, rank + rot
+    lens, starts = [301, 7, 1, 64, 130, 2], [0, 40, 500, 17, 222, 0]
+    g = torch.Generator().manual_seed(heads * 1000 + rank)
+    pages_of = [-(-(s + n) // page) for s, n in zip(starts, lens)]
+    order = torch.randperm(sum(pages_of) + 2, generator=g)
+    table = torch.zeros(len(lens), max(pages_of), dtype=torch.int32)
+    at = 0
+    for r, n in enumerate(pages_of):
+        table[r, :n] = order[at:at + n]
+        at += n
+    cache = torch.randn(sum(pages_of) + 2, 1, 1, page, D, generator=g).to(torch.bfloat16)
+    cache[..., :rank] *= 0.5
+    tokens = sum(lens)
+    q_abs = torch.randn(tokens, heads, rank, generator=g) * 0.4
+    q_rot = (torch.randn(tokens, heads, rot, generator=g) * 0.4).to(torch.bfloat16)
+    token_req = torch.cat([torch.full((n,), r) for r, n in enumerate(lens)]).to(torch.int32)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(torch.int32)
+
+    def row(r, key):
+        return cache[int(table[r, key // page]), 0, 0, key % page]
+
+    # a query that points at one key: far back, or one key outside the window
+    first = {r: sum(lens[:r]) for r in range(len(lens))}
+    for r in (0, 4):
+        t = first[r] + lens[r] - 3
+        key = 1 if not window else int(pos[t]) - window
+        q_abs[t, 0] = 6.0 * row(r, key)[:rank].float() / row(r, key)[:rank].float().norm()
+    scale = 0.7 * D ** -0.5
+    want = torch.zeros(tokens, heads, rank, dtype=torch.float64)
+    keys = {}
+    for r in range(len(lens)):
+        keys[r] = torch.stack([row(r, k) for k in range(starts[r] + lens[r])]).double()
+    for t in range(tokens):
+        r, p = int(token_req[t]), int(pos[t])
+        lo = max(0, p - window + 1) if window else 0
+        k = keys[r][lo:p + 1]
+        s = (q_abs[t].double() @ k[:, :rank].T + q_rot[t].double() @ k[:, rank:].T) * scale
+        want[t] = torch.softmax(s, -1) @ k[:, :rank]
+    got = ops.latent_attention(q_abs.to(DEV), q_rot.to(DEV), cache.to(DEV), table.to(DEV),
+                               token_req.to(DEV), pos.to(DEV), heads, rank, rot, page, window,
+                               scale, max_keys=max(s + n for s, n in zip(starts, lens)),
+                               entries=len(lens))
+    close(got, want, "float32", "rows of several tokens", f32=2e-4)
+    alone = ops.latent_attention(q_abs.to(DEV), q_rot.to(DEV), cache.to(DEV), table.to(DEV),
+                                 token_req.to(DEV), pos.to(DEV), heads, rank, rot, page, window,
+                                 scale, max_keys=max(s + n for s, n in zip(starts, lens)))
+    close(alone, want, "float32", "a token a block", f32=2e-4)
+
+
 # ------------------------------------------------------------------ whole models
 @pytest.fixture(scope="module")
 def mixed_model():
@@ -511,6 +570,24 @@ def test_long_decoding_past_many_windows(dtype):
     got = U.run_schedule(st, {"r": toks}, [[("r", 10)]] + [[("r", 1)]] * 400)
     U.assert_close(got["r"], want, dtype, "long decoding")
     assert st.graph_replays == 400
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_in_one_step(dtype):
+    """Two prompts of some hundred tokens in one step (what the prompt forms of the attention
+    kernels take: several tokens a block, a portion ending inside a block), a third admitted
+    beside their decoding."""
+    cfg = U.config([U.layer(U.latent(4, 16, 16, 16, 64, 32, base=1000.0, scale=0.3), U.dense(64)),
+                    U.layer(U.attention(4, 2, 32, size=150, conv=3, scale=0.25), U.dense(48)),
+                    U.layer(U.latent(6, 8, 16, 24, 64, 24, kv_from=0, scale=0.35), None)],
+                   width=64, vocab=120)
+    weights = U.random_weights(cfg, 41)
+    reqs = {"x": U.tokens(cfg, 333, 1), "y": U.tokens(cfg, 301, 2), "z": U.tokens(cfg, 310, 3)}
+    want = {r: U.plain_logits(cfg, weights, t) for r, t in reqs.items()}
+    st = stepper_for(U.load(cfg, weights, dtype), page_size=16, num_pages=64, num_slots=3)
+    got = U.run_schedule(st, reqs, [[("x", 330), ("y", 299)], [("x", 1), ("y", 1), ("z", 309)],
+                                    [("x", 2), ("y", 1), ("z", 1)]])
+    check_all(got, want, dtype, "long prompts")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
