@@ -32,6 +32,11 @@ class ModelConfig:
     def layout(self) -> ModelLayout:
         raise NotImplementedError
 
+    def with_shapes(self, shape_of) -> "ModelConfig":
+        """Take sizes that config.json leaves to the tensors: ``shape_of(name)`` returns the
+        shape of a checkpoint tensor or None.  Most configurations need none."""
+        return self
+
     # Tokens that end a request, from config.json (eos_token_id may be a list).
     def stop_token_ids(self) -> tuple[int, ...]:
         return ()

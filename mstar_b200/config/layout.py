@@ -78,7 +78,14 @@ class AttentionSpec:
     sequence are per-request state.  ``value_from_key``: there is no value projection, a key
     head as it leaves the convolution (before its norm) is the value.  ``head_gate``: the
     output of head h is multiplied by ``sigmoid(W_g x)_h``, one number a head, before the
-    output product.
+    output product; ``feature_gate``: the concatenated heads are multiplied feature by feature
+    by ``sigmoid(W_g x)`` (W_g has ``num_heads * value_dim`` rows).  ``qk_norm_whole``: the
+    RMS norm runs over all heads of q (and of k) at once, with one weight per feature of the
+    whole projection.  A rope position spec with ``interleaved`` pairs feature 2i with 2i + 1.
+    ``q_temp``: (coef, every) multiplies the query at position p by ``1 + coef * ln(floor((p
+    + 1) / every) + 1)``.  ``softcap``: scores become ``softcap * tanh(score / softcap)`` after
+    the scale.  ``sink``: "learned" puts ``exp(sink_h)``, a parameter a head, into the
+    softmax's denominator (it has no key and no value); "zero" puts exp(0) = 1 there.
     """
 
     kind: str = "attention"
@@ -97,6 +104,11 @@ class AttentionSpec:
     conv_taps: int = 0
     value_from_key: bool = False
     head_gate: bool = False
+    feature_gate: bool = False
+    qk_norm_whole: bool = False
+    q_temp: Optional[tuple] = None
+    softcap: Optional[float] = None
+    sink: Optional[str] = None
 
     @property
     def value_dim(self) -> int:
@@ -107,18 +119,20 @@ class AttentionSpec:
         """Whether this is the attention that the kernels of the dense decoder take."""
         return (not self.keep_first and self.v_head_dim in (None, self.head_dim)
                 and not self.bias and self.qk_norm_eps is None and self.conv_taps == 0
-                and not self.value_from_key and not self.head_gate)
+                and not self.value_from_key and not self.head_gate and not self.feature_gate
+                and self.q_temp is None and self.softcap is None and self.sink is None)
 
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
     """``down(act(gate(x)) * up(x))`` with a fused ``[gate; up]`` matrix; ``activation``:
-    "silu" or "gelu_tanh"."""
+    "silu" or "gelu_tanh".  ``bias``: the three products add a bias."""
 
     kind: str = "gated_mlp"
     hidden_size: int = 0
     intermediate_size: int = 0
     activation: str = "silu"
+    bias: bool = False
 
 
 @dataclass(frozen=True)
@@ -156,13 +170,47 @@ class SelectiveScanSpec:
 
 @dataclass(frozen=True)
 class ParallelMixerSpec:
-    """kind "parallel": several mixers side by side on the same input; the result is the mean
-    of their outputs, each RMS-normed over the model width with a weight of its own."""
+    """kind "parallel": several mixers side by side on the same input.  ``merge``
+    "mean_of_norms": the result is the mean of their outputs, each RMS-normed over the model
+    width with a weight of its own; "weighted_sum": ``sum_b scales[b] * branch_b``."""
 
     kind: str = "parallel"
     hidden_size: int = 0
     branches: tuple = ()
     norm_eps: float = 1e-6
+    shares_kv: bool = False
+    merge: str = "mean_of_norms"
+    scales: tuple = ()
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """kind "gated_delta": a delta-rule matrix memory with a decay per head and key channel,
+    carried from token to token as per-request state.
+
+    ``q = W_q h`` and ``k = W_k h`` have ``num_kv_heads`` heads of ``qk_dim``, ``v = W_v h`` has
+    ``num_heads`` heads of ``v_dim``; head h reads q/k head ``h // (num_heads / num_kv_heads)``.
+    Each passes a causal convolution of ``conv`` taps per channel and SiLU; q and k become
+    unit vectors per head (``x / sqrt(sum x^2 + unit_eps)``), q times ``qk_dim ** -0.5``.
+    ``beta = sigmoid(W_b h)`` a head; ``decay = exp(-exp(A_log_h) * softplus(W_a2 W_a1 h +
+    dt_bias))`` a head and key channel.  Per head, in this order: ``S = decay * S`` row by
+    row, ``u = beta (v - S^T k)``, ``S += k u^T``, ``o = S^T q``.  Each head's o is divided by
+    its root mean square (``norm_eps``), scaled by a weight shared by the heads, gated by
+    ``sigmoid(W_g2 W_g1 h)`` and projected back.  S (float) and the convolutions' last
+    ``conv - 1`` inputs are per-request state.
+    """
+
+    kind: str = "gated_delta"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    conv: int = 1
+    decay_rank: int = 0
+    gate_rank: int = 0
+    norm_eps: float = 1e-6
+    unit_eps: float = 1e-6
     shares_kv: bool = False
 
 
@@ -286,6 +334,12 @@ class BlockSpec:
     kind "postnorm": ``h += residual_mult * norm1_post(mixer(h)); h += residual_mult *
     norm2_post(ffn(h))``: the sublayers read the residual itself (``norm1`` and ``norm2`` are
     None), only their outputs are normed.
+    kind "hyper": hyper-connections.  The residual is ``streams`` copies ``x_1 .. x_s`` (all
+    equal to the embedding output at first); sublayer q reads ``norm_q(sum_s in_q[s] x_s)``
+    and then, all copies at once from the old ones, ``x_t = sum_s mix_q[s, t] x_s +
+    residual_mult * out_q[t] * y``; the model's residual is the sum of the copies.  ``streams``
+    0 is the plain ``x += residual_mult * sublayer(norm(x))`` through the same kernels.
+    ``ffn`` None leaves the second sublayer out.
     ``mixer`` / ``ffn`` are any registered spec; they may differ from block
     to block within one model.
     """
@@ -298,6 +352,7 @@ class BlockSpec:
     norm1_post: Optional[NormSpec] = None
     norm2_post: Optional[NormSpec] = None
     residual_mult: float = 1.0
+    streams: int = 0
 
 
 @dataclass(frozen=True)

@@ -103,3 +103,8 @@ def _register_builtin() -> None:
 
     if "Relurax" not in _ARCHITECTURES:
         register_architecture("Relurax", ReluraxConfig, relurax_checkpoint_map)
+    from ..weights.mokotar import mokotar_checkpoint_map
+    from .mokotar import MokotarConfig
+
+    if "Mokotar" not in _ARCHITECTURES:
+        register_architecture("Mokotar", MokotarConfig, mokotar_checkpoint_map)

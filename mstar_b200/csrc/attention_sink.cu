@@ -9,12 +9,19 @@
 //             its norm, is written as the value head;
 //             every q and k head is divided by its root mean square (eps inside the root)
 //             and scaled by a weight shared by the heads; the first `rot` features of q and
-//             k are rotated (feature i with i + rot/2, angle position * freq[i]); q goes to
-//             a dense [tokens, nq*hd] buffer, k and v into the token's cache page.
+//             k are rotated (feature i with i + rot/2, or, `interleaved`, feature 2i with
+//             2i + 1; angle position * freq[i]); q goes to a dense [tokens, nq*hd] buffer, k
+//             and v into the token's cache page.  With `norm_whole` the root mean square is
+//             taken over all heads of q (and of k) at once and the weights have a number per
+//             feature of the whole projection.  With `temp_every` > 0 the query is multiplied
+//             by 1 + temp_coef * ln(floor((position + 1) / temp_every) + 1).
 //   attend    the token whose key sits at cache position p sees keys j <= p with
 //             p - j < window or j < keep_first (window 0: every j <= p): the keys
 //             [0, min(keep_first, lo)) and [lo, p], lo = max(0, p - window + 1).  Softmax over
-//             them, scores q.k * scale, float statistics and sums.
+//             them, scores q.k * scale, float statistics and sums.  With `softcap` > 0 a
+//             score becomes softcap * tanh(score / softcap); with `sink` the denominator of
+//             head h also holds exp(sink[h]), which has no key and no value; a gate per
+//             feature multiplies the output by sigmoid(gate[t][h * vd + d]).
 //
 // A cache page is [nkv][page_size][hd] keys followed by [nkv][page_size][vd] values.
 // Norms, angles, scores, probabilities and output sums are float for both activation types.
@@ -29,6 +36,10 @@ struct PrepArgs {
     int taps;       // 0: no convolution
     int v_from_k;   // 1: the values are the key heads before their norm
     long long state_stride;     // floats between the state of two slots
+    int interleaved;            // 1: feature 2i is rotated with 2i + 1
+    int norm_whole;             // 1: one root mean square over all q heads, one over all k heads
+    float temp_coef;
+    int temp_every;             // 0: no query temperature
 };
 
 // The convolved value of channel `col` (a column of q or k) of token t, the i-th of its
@@ -72,6 +83,7 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
     const int half = a.rot / 2;
     float* cs = sm;                            // [half] cosines, [half] sines
     float* heads = sm + 2 * half;              // [warps][hd]
+    __shared__ float red[32];
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nwarps = blockDim.x >> 5;
     const unsigned long long waited = pdl_wait();
@@ -104,6 +116,23 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
     A* page_base = kv_cache + (size_t)page * page_elems;
     float* mine = heads + warp * a.hd;
     const int nheads = a.v_from_k ? a.nq + a.nkv : a.nq + 2 * a.nkv;
+    float inv_whole_q = 1.f, inv_whole_k = 1.f;
+    if (a.norm && a.norm_whole) {              // (no convolution in this form)
+        float sq = 0.f, sk = 0.f;
+        const int nqd = a.nq * a.hd, nkd = a.nkv * a.hd;
+        for (int i = threadIdx.x; i < nqd + nkd; i += blockDim.x) {
+            float v = row[i];
+            if (bias != nullptr) v += to_float(bias[i]);
+            if (i < nqd) sq = fmaf(v, v, sq); else sk = fmaf(v, v, sk);
+        }
+        sq = block_sum(sq, red);
+        sk = block_sum(sk, red);
+        inv_whole_q = rsqrtf(sq / (float)nqd + a.eps);
+        inv_whole_k = rsqrtf(sk / (float)nkd + a.eps);
+    }
+    float q_mult = 1.f;
+    if (a.temp_every > 0)
+        q_mult = 1.f + a.temp_coef * logf((float)((positions[t] + 1) / a.temp_every) + 1.f);
     // few tokens (decoding): the heads of a token are dealt out among gridDim.y blocks
     for (int h = blockIdx.y * nwarps + warp; h < nheads; h += nwarps * gridDim.y) {
         if (h >= a.nq + a.nkv) {               // a value head: bias, then the page
@@ -140,17 +169,30 @@ sink_prepare_kernel(const float* __restrict__ qkv, const W* __restrict__ bias,
             ss = fmaf(v, v, ss);
         }
         ss = warp_sum(ss);
-        const float inv = a.norm ? rsqrtf(ss / (float)a.hd + a.eps) : 1.f;
+        float inv = a.norm ? rsqrtf(ss / (float)a.hd + a.eps) : 1.f;
         const W* nw = is_q ? q_norm : k_norm;
+        if (a.norm && a.norm_whole) {
+            inv = is_q ? inv_whole_q : inv_whole_k;
+            nw += (size_t)(is_q ? h : h - a.nq) * a.hd;
+        }
+        const float mult = is_q ? q_mult : 1.f;
         __syncwarp();
         if (a.norm)
-            for (int d = lane; d < a.hd; d += 32) mine[d] = mine[d] * inv * to_float(nw[d]);
+            for (int d = lane; d < a.hd; d += 32) mine[d] = mine[d] * inv * to_float(nw[d]) * mult;
+        else if (mult != 1.f)
+            for (int d = lane; d < a.hd; d += 32) mine[d] *= mult;
         __syncwarp();
         A* dst = is_q ? q_out + (size_t)t * a.q_stride_out + (size_t)h * a.hd
                       : page_base + ((size_t)(h - a.nq) * a.page_size + slot) * a.hd;
         for (int d = lane; d < a.hd; d += 32) {
             float v = mine[d];
-            if (d < half) {
+            if (a.interleaved) {
+                if (d < a.rot) {
+                    const int i = d >> 1;
+                    v = (d & 1) ? mine[d] * cs[i] + mine[d - 1] * cs[half + i]
+                                : mine[d] * cs[i] - mine[d + 1] * cs[half + i];
+                }
+            } else if (d < half) {
                 v = mine[d] * cs[d] - mine[d + half] * cs[half + d];
             } else if (d < a.rot) {
                 const int i = d - half;
@@ -170,8 +212,10 @@ MSTAR_API int mstar_sink_prepare(const float* qkv, const void* bias, const void*
                                  int vd, int rot, int page_size, float eps, int norm,
                                  int row_stride, const void* conv_q, const void* conv_k, int taps,
                                  int v_from_k, const int* qo_indptr, const int* slots,
-                                 const float* state, long long state_stride, void* stream) {
+                                 const float* state, long long state_stride, int interleaved,
+                                 int norm_whole, float temp_coef, int temp_every, void* stream) {
     if (tokens <= 0) return 0;
+    if (norm_whole && taps > 0) return -1;
     if (hd <= 0 || vd <= 0 || rot < 0 || rot > hd || (rot & 1) || nq <= 0 || nkv <= 0) return -1;
     if (taps < 0 || (v_from_k && vd != hd)) return -1;
     if (taps > 0 && (bias != nullptr || !conv_q || !conv_k || !qo_indptr)) return -1;
@@ -181,7 +225,7 @@ MSTAR_API int mstar_sink_prepare(const float* qkv, const void* bias, const void*
     const size_t smem = sizeof(float) * ((size_t)rot + (size_t)(threads / 32) * hd);
     if (smem > 48 * 1024) return -1;
     PrepArgs a{nq, nkv, hd, vd, rot, page_size, bt_stride, nq * hd, eps, norm, row_stride, taps,
-               v_from_k, state_stride};
+               v_from_k, state_stride, interleaved, norm_whole, temp_coef, temp_every};
     cudaStream_t s = (cudaStream_t)stream;
     // a block takes 8 heads at a time: with fewer blocks than SMs, a token's heads go to
     // several blocks (each makes the token's sines and cosines for itself)
@@ -251,6 +295,10 @@ MSTAR_API int mstar_conv_state_advance(const float* qkv, int row_stride, int cha
 struct SinkArgs {
     int nq, nkv, hd, vd, page_size, bt_stride, window, keep_first, q_stride;
     float scale;
+    float softcap;              // 0: none
+    const float* sink;          // null, or one number a query head
+    const float* gate;          // null, or float rows with a number per (head, feature)
+    int gate_stride;
 };
 
 // The v-th key a token sees: the kept first keys come before the window's.
@@ -282,6 +330,7 @@ sink_attention_generic_kernel(const A* __restrict__ q, A* __restrict__ out,
     const unsigned long long waited = pdl_wait();
     q = pdl_after(q, waited);
     kv_cache = pdl_after(kv_cache, waited);
+    const float* gate = pdl_after(a.gate, waited);
     const int hi = cache_pos[t] + 1;
     const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
     const int kept = a.keep_first < lo ? a.keep_first : lo;
@@ -325,6 +374,7 @@ sink_attention_generic_kernel(const A* __restrict__ q, A* __restrict__ out,
                 float dot = 0.f;
                 for (int d = 0; d < hd; ++d) dot = fmaf(qv[d], kv[d], dot);
                 s = dot * a.scale;
+                if (a.softcap > 0.f) s = a.softcap * tanhf(s / a.softcap);
             }
             sc[idx] = s;
         }
@@ -371,11 +421,20 @@ sink_attention_generic_kernel(const A* __restrict__ q, A* __restrict__ out,
         __syncthreads();
     }
 
+    if (a.sink != nullptr) {                  // the sink joins the denominator only
+        for (int g = tid; g < G; g += SA_THREADS) l_s[g] += expf(a.sink[kvh * G + g] - m_s[g]);
+        __syncthreads();
+    }
     A* orow = out + (size_t)t * a.nq * vd + (size_t)kvh * G * vd;
 #pragma unroll
     for (int k = 0; k < SA_MAX_ACC; ++k) {
         const int o = tid + k * SA_THREADS;
-        if (o < n_out) orow[o] = from_float<A>(acc[k] / l_s[o / vd]);
+        if (o < n_out) {
+            float r = acc[k] / l_s[o / vd];
+            if (gate != nullptr)
+                r /= 1.f + expf(-gate[(size_t)t * a.gate_stride + (size_t)kvh * G * vd + o]);
+            orow[o] = from_float<A>(r);
+        }
     }
 }
 
@@ -387,7 +446,8 @@ MSTAR_API int mstar_sink_attention_generic(const void* q, int q_stride, void* ou
                                            const int* cache_pos, int tokens, int nq, int nkv,
                                            int hd, int vd, int page_size, int window,
                                            int keep_first, float scale, int act_dtype,
-                                           void* stream) {
+                                           float softcap, const float* sink, const float* gate,
+                                           int gate_stride, void* stream) {
     if (tokens <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || hd <= 0 || vd <= 0) return -1;
     const int G = nq / nkv;
@@ -397,7 +457,8 @@ MSTAR_API int mstar_sink_attention_generic(const void* q, int q_stride, void* ou
                                          (size_t)G * SA_TILE + 3 * (size_t)G);
     if (smem > 200 * 1024) return -1;
     cudaStream_t s = (cudaStream_t)stream;
-    SinkArgs a{nq, nkv, hd, vd, page_size, bt_stride, window, keep_first, q_stride, scale};
+    SinkArgs a{nq, nkv, hd, vd, page_size, bt_stride, window, keep_first, q_stride, scale,
+               softcap, sink, gate, gate_stride};
     dim3 grid(tokens, nkv);
     static size_t configured_f32 = 0, configured_bf16 = 0;
     if (act_dtype == MSTAR_F32) {

@@ -12,6 +12,11 @@
 // float exactly, so that the weights stay 32-bit; O is float.  Key and value sizes are
 // padded with zeros in shared memory to the next compiled size D.
 //
+// Options: a soft cap (a score becomes cap * tanh(score / cap) after the scale), a sink a
+// query head (exp(sink_h) joins the softmax's denominator where a row's last partial sums
+// meet; it has no key and no value), and a gate on the output, one number a head or one a
+// feature.
+//
 // With few rows (decoding) the visited keys are shared among `splits` CTAs, each leaving an
 // unnormalised partial (o, running maximum, sum) in scratch, and a second kernel merges.
 #include "common.cuh"
@@ -31,13 +36,28 @@ struct SinkTcArgs {
     float* scratch;
     int q_stride, bt_stride, nq, nkv, hd, vd, page_size, window, keep_first, splits;
     float scale_log2e;
-    // not null: the output of head h of token t is multiplied by sigmoid(gate[t * gate_stride + h])
+    // not null: the output of head h of token t is multiplied by sigmoid(gate[t * gate_stride + h]),
+    // or, with gate_features, feature d of it by sigmoid(gate[t * gate_stride + h * vd + d])
     const float* gate;
     int gate_stride;
+    int gate_features;
+    float scale, softcap;       // softcap 0: none
+    const float* sink;          // null, or one number a query head
 };
 
 __device__ __forceinline__ float st_head_gate(const float* gate, int stride, int tok, int head) {
     return gate == nullptr ? 1.f : 1.f / (1.f + expf(-gate[(size_t)tok * stride + head]));
+}
+// The gate of one output feature: per head (features 0), or per feature.
+__device__ __forceinline__ float st_gate(const float* gate, int stride, int features, int vd, int tok,
+                                         int head, int d) {
+    if (gate == nullptr) return 1.f;
+    const size_t i = (size_t)tok * stride + (features ? (size_t)head * vd + d : (size_t)head);
+    return 1.f / (1.f + expf(-gate[i]));
+}
+// What a sink adds to a denominator whose terms are 2^(s - m), m in the base-2 domain.
+__device__ __forceinline__ float st_sink_term(const float* sink, int head, float m) {
+    return sink == nullptr ? 0.f : exp2f(sink[head] * 1.4426950408889634f - m);
 }
 
 template <int D> __device__ __forceinline__ int st_off(int row, int c) { return row * (D + 8) + c * 8; }
@@ -184,7 +204,12 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                     const bool upper = q4 < 2;
                     const int cp = upper ? cpA : cpB;
                     const bool ok = v < visible && key <= cp && (cp - key < W || key < a.keep_first);
-                    const float sv = ok ? s[j][q4] * a.scale_log2e : -INFINITY;
+                    float sv = -INFINITY;
+                    if (ok) {
+                        sv = a.softcap > 0.f
+                                 ? a.softcap * tanhf(s[j][q4] * a.scale / a.softcap) * 1.4426950408889634f
+                                 : s[j][q4] * a.scale_log2e;
+                    }
                     s[j][q4] = sv;
                     if (upper) mx0 = fmaxf(mx0, sv); else mx1 = fmaxf(mx1, sv);
                 }
@@ -302,8 +327,9 @@ sink_attention_tc_kernel(SinkTcArgs a) {
             const int tok = q_start + row / G, head = kvh * G + row % G;
             if (a.splits == 1) {
                 if (d < a.vd)
-                    a.out[((size_t)tok * a.nq + head) * a.vd + d] =
-                        __float2bfloat16_rn(sum / L * st_head_gate(gate, a.gate_stride, tok, head));
+                    a.out[((size_t)tok * a.nq + head) * a.vd + d] = __float2bfloat16_rn(
+                        sum / (L + st_sink_term(a.sink, head, M)) *
+                        st_gate(gate, a.gate_stride, a.gate_features, a.vd, tok, head, d));
             } else {
                 float* dst = a.scratch + (((size_t)tok * a.nq + head) * a.splits + split) * pw;
                 dst[d] = d < a.vd ? sum : (d == a.vd ? M : L);
@@ -317,13 +343,21 @@ sink_attention_tc_kernel(SinkTcArgs a) {
         const float l = half ? l1 : l0, m = half ? m1 : m0;
         const int tok = q_start + row / G, head = kvh * G + row % G;
         if (a.splits == 1) {
-            const float inv = st_head_gate(gate, a.gate_stride, tok, head) / l;
+            const float denom = l + st_sink_term(a.sink, head, m);
+            const float inv = (a.gate_features ? 1.f : st_head_gate(gate, a.gate_stride, tok, head)) / denom;
             bf16* dst = a.out + ((size_t)tok * a.nq + head) * a.vd + (lane & 3) * 2;
 #pragma unroll
             for (int n = 0; n < D / 8; ++n)
-                if (n * 8 < a.vd)
+                if (n * 8 < a.vd) {
+                    float g0 = 1.f, g1 = 1.f;
+                    if (a.gate_features) {
+                        const int d = n * 8 + (lane & 3) * 2;
+                        g0 = st_gate(gate, a.gate_stride, 1, a.vd, tok, head, d);
+                        g1 = st_gate(gate, a.gate_stride, 1, a.vd, tok, head, d + 1);
+                    }
                     *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) =
-                        __floats2bfloat162_rn(o[n][2 * half] * inv, o[n][2 * half + 1] * inv);
+                        __floats2bfloat162_rn(o[n][2 * half] * inv * g0, o[n][2 * half + 1] * inv * g1);
+                }
         } else {
             float* dst = a.scratch + (((size_t)tok * a.nq + head) * a.splits + split) * (a.vd + 2);
 #pragma unroll
@@ -347,7 +381,7 @@ sink_attention_tc_kernel(SinkTcArgs a) {
 // splits in flight together.
 __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __restrict__ out,
                                   int rows, int vd, int splits, const float* gate, int gate_stride,
-                                  int nq) {
+                                  int nq, int gate_features, const float* __restrict__ sink) {
     const unsigned long long waited = pdl_wait();
     scratch = pdl_after(scratch, waited);
     gate = pdl_after(gate, waited);
@@ -365,7 +399,8 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
     }
     const float M = warp_max(fmaxf(m_a, m_b));
     const float w_a = exp2f(m_a - M), w_b = exp2f(m_b - M);   // 0 for a split that saw no key
-    const float L = warp_sum(l_a * w_a + l_b * w_b) / st_head_gate(gate, gate_stride, row / nq, row % nq);
+    const float L = (warp_sum(l_a * w_a + l_b * w_b) + st_sink_term(sink, row % nq, M)) /
+                    (gate_features ? 1.f : st_head_gate(gate, gate_stride, row / nq, row % nq));
     for (int d0 = 0; d0 < vd; d0 += 32) {
         const int d = d0 + lane;
         float sum = 0.f;
@@ -374,7 +409,9 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
             const float w = __shfl_sync(0xffffffffu, s < 32 ? w_a : w_b, s & 31);
             if (d < vd) sum = fmaf(base[(size_t)s * (vd + 2) + d], w, sum);
         }
-        if (d < vd) out[(size_t)row * vd + d] = __float2bfloat16_rn(sum / L);
+        if (d < vd)
+            out[(size_t)row * vd + d] = __float2bfloat16_rn(
+                sum / L * (gate_features ? st_gate(gate, gate_stride, 1, vd, row / nq, row % nq, d) : 1.f));
     }
 }
 
@@ -419,7 +456,8 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
                                       const int* kv_len, int entries, int tokens, int max_q_len,
                                       int nq, int nkv, int hd, int vd, int page_size, int window,
                                       int keep_first, float scale, int splits, float* scratch,
-                                      const float* gate, int gate_stride, void* stream) {
+                                      const float* gate, int gate_stride, int gate_features,
+                                      float softcap, const float* sink, void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || entries > 65535 || nkv > 65535) return -1;
     if (hd % 8 || vd % 8 || hd <= 0 || vd <= 0 || hd > 256 || vd > 256 || splits < 1 || splits > 64)
@@ -446,6 +484,10 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
     a.scale_log2e = scale * 1.4426950408889634f;
     a.gate = gate;
     a.gate_stride = gate_stride;
+    a.gate_features = gate != nullptr && gate_features;
+    a.scale = scale;
+    a.softcap = softcap;
+    a.sink = sink;
     cudaStream_t s = (cudaStream_t)stream;
     const int wide = hd > vd ? hd : vd;
     int code;
@@ -457,6 +499,6 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
     if (code != 0 || splits == 1) return code;
     const int rows = tokens * nq;
     mstar_launch(sink_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, s, (const float*)scratch,
-                 (bf16*)out, rows, vd, splits, gate, gate_stride, nq);
+                 (bf16*)out, rows, vd, splits, gate, gate_stride, nq, a.gate_features, sink);
     return launch_status();
 }

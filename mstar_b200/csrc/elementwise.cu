@@ -288,6 +288,46 @@ MSTAR_API int mstar_silu_mul(const void* gate_up, void* out, int act_dtype, int 
     return launch_status();
 }
 
+// out = act(gate + bias_gate) * (up + bias_up) from the float product [rows][2 * inter]
+// (gate columns first) and a bias of 2 * inter numbers; float arithmetic, the result in the
+// activation type.
+template <typename A, typename W>
+__global__ void bias_act_mul_kernel(const float* gate_up, const W* __restrict__ bias,
+                                    A* __restrict__ out, int inter, size_t total, int kind) {
+    gate_up = pdl_after(gate_up, pdl_wait());
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = idx / inter;
+        const int col = (int)(idx - row * inter);
+        const float* p = gate_up + row * 2 * (size_t)inter;
+        const float g = p[col] + to_float(bias[col]);
+        const float u = p[inter + col] + to_float(bias[inter + col]);
+        out[idx] = from_float<A>(plain_activation(g, kind) * u);
+    }
+}
+
+MSTAR_API int mstar_bias_act_mul(const float* gate_up, const void* bias, int weight_dtype, void* out,
+                                 int act_dtype, int rows, int inter, int kind, void* stream) {
+    const size_t total = (size_t)rows * inter;
+    if (total == 0) return 0;
+    if ((kind != 1 && kind != 2) || bias == nullptr) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    const size_t most = (size_t)device_sm_count() * 32;   // a grid-stride loop takes the rest
+    if (blocks > most) blocks = most;
+#define GO(A, W)                                                                                  \
+    mstar_launch((bias_act_mul_kernel<A, W>), dim3((int)blocks), dim3(threads), 0, s, gate_up,   \
+                 (const W*)bias, (A*)out, inter, total, kind)
+    if (act_dtype == MSTAR_F32) {
+        if (weight_dtype == MSTAR_F32) { GO(float, float); } else { GO(float, bf16); }
+    } else {
+        if (weight_dtype == MSTAR_F32) { GO(bf16, float); } else { GO(bf16, bf16); }
+    }
+#undef GO
+    return launch_status();
+}
+
 // ------------------------------------------------- logit scale and soft cap
 // x = x * scale, then x = cap * tanh(x / cap) when cap > 0; float, in place.
 __global__ void scale_softcap_kernel(float* __restrict__ x, size_t n, float scale, float cap) {

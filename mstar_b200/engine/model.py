@@ -112,7 +112,7 @@ class Model:
         if want_rows is None or want_rows.numel() == 0:
             return torch.empty((0, self.vocab_size), dtype=torch.float32,
                                device=self.runtime.device)
-        rows = ops.gather_add_rows(stream.h, stream.take_delta(), want_rows)
+        rows = stream.gather(want_rows)
         x = self.final_norm.norm_rows(rows)
         return self.head.forward(x)
 
@@ -145,6 +145,11 @@ def load_model(source, dtype="bfloat16", device="cuda:0", *, config: Optional[Mo
                            "(sm_100a) GPU")
     if config is None:
         config = load_config(source)
+    # sizes that the configuration leaves to the tensors' shapes
+    from ..weights.loader import checkpoint_shapes
+
+    config = config.with_shapes(checkpoint_shapes(tensors if tensors is not None
+                                                  else Path(source)))
     layout = config.layout()
     arch = get_architecture(config.architecture)
     specs = model_param_specs(layout)

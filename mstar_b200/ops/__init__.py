@@ -131,6 +131,24 @@ def silu_mul(gate_up: torch.Tensor, out=None, kind: str = "silu"):
     return out
 
 
+def bias_act_mul(gate_up: torch.Tensor, bias: torch.Tensor, out_dtype: torch.dtype,
+                 kind: str = "silu") -> torch.Tensor:
+    """act(gate_up[:, :I] + bias[:I]) * (gate_up[:, I:] + bias[I:]) from the float product
+    ``gate_up``; the result has ``out_dtype``."""
+    _need_cuda(gate_up, bias)
+    if kind not in GATE_ACTIVATIONS:
+        raise KernelError(f"gate activation {kind!r} has no kernel (known: "
+                          f"{sorted(GATE_ACTIVATIONS)})")
+    assert gate_up.dtype == torch.float32 and gate_up.dim() == 2 and gate_up.is_contiguous()
+    assert gate_up.shape[1] % 2 == 0 and bias.numel() == gate_up.shape[1] and bias.is_contiguous()
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    out = torch.empty((rows, inter), dtype=out_dtype, device=gate_up.device)
+    check(lib.get("elementwise").mstar_bias_act_mul(
+        gate_up.data_ptr(), bias.data_ptr(), _dt(bias), out.data_ptr(), _DT[out_dtype], rows,
+        inter, GATE_ACTIVATIONS[kind], _stream()), "bias_act_mul")
+    return out
+
+
 def convert(src: torch.Tensor, dtype: torch.dtype):
     _need_cuda(src)
     if src.dtype == dtype:
@@ -1207,7 +1225,9 @@ def sink_page_elements(num_kv_heads: int, page_size: int, head_dim: int, v_dim: 
 def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache_pos, token_req,
                  block_table, kv_cache: torch.Tensor, num_heads: int, num_kv_heads: int,
                  head_dim: int, v_dim: int, rot: int, page_size: int, eps: float,
-                 out_dtype: torch.dtype, conv=None, value_from_key: bool = False) -> torch.Tensor:
+                 out_dtype: torch.dtype, conv=None, value_from_key: bool = False,
+                 interleaved: bool = False, norm_whole: bool = False,
+                 q_temp=None) -> torch.Tensor:
     """From the float fused projection ``qkv`` [tokens, (heads + kv_heads) * head_dim +
     kv_heads * v_dim (+ columns this kernel does not read)]: add ``bias``, norm every query
     and key head (``q_norm`` / ``k_norm`` weights of ``head_dim``, or None for no norm), rotate
@@ -1218,9 +1238,19 @@ def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache
     qo_indptr, slots, state) puts a causal convolution over time on every q and k channel
     before the norm; the rows before a portion come from ``state`` [slots, (taps - 1) *
     channels] (float), which ``conv_state_advance`` moves on afterwards.  ``value_from_key``:
-    the row has no value part; a key head before its norm is the value head."""
+    the row has no value part; a key head before its norm is the value head.
+    ``interleaved``: feature 2i is rotated with 2i + 1 instead of i with i + rot / 2.
+    ``norm_whole``: one root mean square over all query heads and one over all key heads;
+    ``q_norm`` / ``k_norm`` then have ``heads * head_dim`` / ``kv_heads * head_dim`` numbers.
+    ``q_temp``: (coef, every) multiplies the query of the token at position p by ``1 + coef
+    * ln(floor((p + 1) / every) + 1)``."""
     _need_cuda(qkv, bias, q_norm, k_norm, freq, positions, cache_pos, token_req, block_table,
                kv_cache)
+    if q_norm is not None:
+        per = (num_heads, num_kv_heads) if norm_whole else (1, 1)
+        assert q_norm.numel() == per[0] * head_dim and k_norm.numel() == per[1] * head_dim
+    assert not (norm_whole and conv is not None)
+    temp_coef, temp_every = (float(q_temp[0]), int(q_temp[1])) if q_temp else (0.0, 0)
     assert qkv.dtype == torch.float32 and qkv.dim() == 2 and qkv.stride(1) == 1
     assert kv_cache.is_contiguous()
     tokens = qkv.shape[0]
@@ -1255,7 +1285,8 @@ def sink_prepare(qkv: torch.Tensor, bias, q_norm, k_norm, freq, positions, cache
         block_table.stride(0), q.data_ptr(), kv_cache.data_ptr(), _DT[out_dtype], tokens, num_heads,
         num_kv_heads, head_dim, v_dim, rot, page_size, float(eps), int(q_norm is not None),
         qkv.stride(0), _ptr(wq), _ptr(wk), taps, int(value_from_key), _ptr(qo), _ptr(slots),
-        _ptr(state) if taps > 1 else 0, state.stride(0) if taps > 1 else 0, _stream())
+        _ptr(state) if taps > 1 else 0, state.stride(0) if taps > 1 else 0, int(interleaved),
+        int(norm_whole and q_norm is not None), temp_coef, temp_every, _stream())
     if code == -1:
         raise KernelError(f"attention input kernel refuses head_dim={head_dim}, v_dim={v_dim}, "
                           f"rot={rot}, taps={taps}")
@@ -1296,21 +1327,31 @@ def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_h
 
 def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_req, cache_pos,
                    num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, page_size: int,
-                   window: int, keep_first: int, scale: float, ctx=None, gate=None) -> torch.Tensor:
+                   window: int, keep_first: int, scale: float, ctx=None, gate=None,
+                   softcap: float | None = None, sink=None) -> torch.Tensor:
     """Softmax attention of every token over the keys it sees: those of the last ``window``
     positions (0: all) and the first ``keep_first`` of the sequence.  ``q``: [tokens, heads *
     head_dim]; returns [tokens, heads * v_dim].  ``gate``: None, or float [tokens, heads] (a
     column view of a wider product): head h's output is multiplied by sigmoid(gate[t, h]),
-    where the tensor-core kernel writes it out, by a kernel of its own after the other.  bfloat16 with sizes that are multiples of 8
+    where the tensor-core kernel writes it out, by a kernel of its own after the other; a gate
+    of [tokens, heads * v_dim] numbers multiplies feature by feature.  ``softcap``: a score
+    becomes ``softcap * tanh(score / softcap)`` after the scale.  ``sink``: float [heads];
+    ``exp(sink[h])`` joins the denominator of head h's softmax (no key, no value).  bfloat16 with sizes that are multiples of 8
     up to 256 and a step context (``ctx``: entries, their token ranges and lengths) runs on
     the tensor cores (MSTAR_SINK_ATTENTION=generic: never); everything else, float32
     included, on the CUDA cores."""
     _need_cuda(q, kv_cache, block_table, token_req, cache_pos, gate)
     assert q.is_contiguous() and kv_cache.is_contiguous() and kv_cache.dtype == q.dtype
     tokens = q.shape[0]
+    gate_features = False
     if gate is not None:
-        assert tuple(gate.shape) == (tokens, num_heads) and gate.stride(1) == 1
-        assert gate.dtype == torch.float32
+        gate_features = gate.shape[1] == num_heads * v_dim and v_dim > 1
+        assert tuple(gate.shape) == (tokens, num_heads * (v_dim if gate_features else 1))
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1
+    if sink is not None:
+        _need_cuda(sink)
+        assert sink.dtype == torch.float32 and sink.numel() == num_heads and sink.is_contiguous()
+    cap = float(softcap or 0.0)
     out = torch.empty((tokens, num_heads * v_dim), dtype=q.dtype, device=q.device)
     if (ctx is not None and q.dtype == torch.bfloat16 and head_dim % 8 == 0 and v_dim % 8 == 0
             and max(head_dim, v_dim) <= 256 and os.environ.get("MSTAR_SINK_ATTENTION") != "generic"):
@@ -1328,7 +1369,8 @@ def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_r
             block_table.stride(0), ctx.qo_indptr.data_ptr(), ctx.kv_len.data_ptr(),
             ctx.num_entries, tokens, ctx.max_q_len, num_heads, num_kv_heads, head_dim, v_dim,
             page_size, int(window or 0), int(keep_first), float(scale), splits, _ptr(scratch),
-            _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+            _ptr(gate), gate.stride(0) if gate is not None else 0, int(gate_features), cap,
+            _ptr(sink), _stream())
         if code == -1:
             raise KernelError(f"tensor-core window attention refuses heads={num_heads}, "
                               f"kv_heads={num_kv_heads}, head_dim={head_dim}, v_dim={v_dim}")
@@ -1340,12 +1382,13 @@ def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_r
         q.data_ptr(), q.stride(0), out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), tokens, num_heads,
         num_kv_heads, head_dim, v_dim, page_size, int(window or 0), int(keep_first), float(scale),
-        _dt(q), _stream())
+        _dt(q), cap, _ptr(sink), _ptr(gate) if gate_features else 0,
+        gate.stride(0) if gate_features else 0, _stream())
     if code == -1:
         raise KernelError(f"window attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
                           f"head_dim={head_dim}, v_dim={v_dim}")
     check(code, "sink_attention")
-    if gate is not None:
+    if gate is not None and not gate_features:
         head_gate_mul(out, gate, num_heads)
     return out
 
@@ -1443,4 +1486,171 @@ def selective_scan(xc: torch.Tensor, xz: torch.Tensor, proj: torch.Tensor, w_dt,
         raise KernelError(f"selective scan refuses inner={inner}, state={n_state}, rank={rank} "
                           "(at most 256 states a channel)")
     check(code, "selective_scan")
+    return out
+
+
+# ------------------------------------------------------------------ hyper-connections
+def hyper_step(x: torch.Tensor, *, init=None, y=None, y2=None, y_scales=(1.0, 1.0), y_bias=None,
+               mix=None, out=None, read=None, norm_weight=None, eps: float = 0.0,
+               out_dtype: torch.dtype | None = None, rows=None):
+    """What lies between two sublayers of a residual kept as copies ``x`` [tokens, S, width]
+    (float, updated in place).
+
+    With ``y`` (a sublayer's output [tokens, width]; ``y_scales[0] * y + y_scales[1] * y2 +
+    y_bias``) every copy is rewritten from the old ones: ``x_t = sum_s mix[s, t] x_s + out[t] *
+    y``.  With ``init`` [tokens, width] the old copies are all that row.  Then either ``read``
+    (float [S]) with ``norm_weight``: returns ``rmsnorm(sum_s read[s] x_s) * norm_weight`` in
+    ``out_dtype``; or ``rows`` (int32 indices): returns float ``sum_s x_s`` of those tokens
+    without writing the copies back."""
+    _need_cuda(x, init, y, y2, y_bias, mix, out, read, norm_weight, rows)
+    assert x.dtype == torch.float32 and x.dim() == 3 and x.is_contiguous()
+    tokens, streams, width = x.shape
+    assert mix.dtype == torch.float32 and mix.numel() == streams * streams and mix.is_contiguous()
+    assert out.dtype == torch.float32 and out.numel() == streams
+    assert (read is None) != (rows is None)
+    act = out_dtype
+    for t in (y, y2):
+        if t is not None:
+            assert tuple(t.shape) == (tokens, width) and t.is_contiguous()
+            assert act is None or t.dtype == act
+            act = t.dtype
+    if init is not None:
+        assert init.dtype == torch.float32 and tuple(init.shape) == (tokens, width)
+        assert init.is_contiguous()
+    wd = F32
+    for w in (y_bias, norm_weight):
+        if w is not None:
+            wd = _dt(w)
+    for w in (y_bias, norm_weight):
+        assert w is None or (_dt(w) == wd and w.is_contiguous() and w.numel() == width)
+    normed = sums = None
+    if read is not None:
+        assert read.dtype == torch.float32 and read.numel() == streams
+        assert norm_weight is not None and out_dtype is not None
+        normed = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+        blocks = tokens
+    else:
+        assert rows.dtype == torch.int32 and rows.is_contiguous()
+        blocks = rows.numel()
+        sums = torch.empty((blocks, width), dtype=torch.float32, device=x.device)
+    code = lib.get("hyper").mstar_hyper_step(
+        x.data_ptr(), _ptr(init), _ptr(y), _ptr(y2), _ptr(y_bias), float(y_scales[0]),
+        float(y_scales[1]), mix.data_ptr(), out.data_ptr(), _ptr(read), _ptr(norm_weight),
+        _ptr(normed), _ptr(rows), _ptr(sums), blocks, streams, width, float(eps),
+        _DT[act or torch.float32], wd, _stream())
+    if code == -1:
+        raise KernelError(f"hyper-connection kernel refuses streams={streams}, width={width}")
+    check(code, "hyper_step")
+    return normed if read is not None else sums
+
+
+class WeightedSum:
+    """``sum_b scales[b] * branches[b]`` of branch outputs, not computed yet: a block that adds
+    it to the residual takes the branches into its own kernel; ``materialize()`` computes it."""
+
+    def __init__(self, branches, scales):
+        self.branches, self.scales = list(branches), [float(s) for s in scales]
+        self.shape, self.dtype = branches[0].shape, branches[0].dtype
+
+    def materialize(self) -> torch.Tensor:
+        acc, scale = self.branches[0], self.scales[0]
+        if len(self.branches) == 1:
+            return weighted_sum2(acc, acc, scale, 0.0)
+        for b, s in zip(self.branches[1:], self.scales[1:]):
+            acc = weighted_sum2(acc, b, scale, s)
+            scale = 1.0
+        return acc
+
+
+def weighted_sum2(y1: torch.Tensor, y2: torch.Tensor, a: float, b: float) -> torch.Tensor:
+    """a * y1 + b * y2 with float sums."""
+    _need_cuda(y1, y2)
+    assert y1.shape == y2.shape and y1.dtype == y2.dtype and y1.is_contiguous() and y2.is_contiguous()
+    out = torch.empty_like(y1)
+    check(lib.get("hyper").mstar_weighted_sum2(y1.data_ptr(), y2.data_ptr(), out.data_ptr(),
+                                               y1.numel(), float(a), float(b), _dt(y1), _stream()),
+          "weighted_sum2")
+    return out
+
+
+# ------------------------------------------------------------------ gated delta rule
+def gated_delta_state_size(heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> int:
+    """Floats of one request's state: the convolutions' last inputs [taps - 1, 2 * kv_heads *
+    dim + heads * vdim], then S^T [heads, vdim, dim]."""
+    return (taps - 1) * (2 * kv_heads * dim + heads * vdim) + heads * vdim * dim
+
+
+def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_proj: torch.Tensor, dt_bias, a_exp,
+                  token_req, qo_indptr, slots, state: torch.Tensor, heads: int, kv_heads: int,
+                  dim: int, vdim: int, taps: int, unit_eps: float):
+    """From the float fused projection ``proj`` [tokens, q | k | v | b | ...]: convolution and
+    SiLU on the q, k and v channels (``conv_w`` [channels, taps]; rows before a portion from
+    ``state``), unit q (times ``dim ** -0.5``) and k per head, ``beta = sigmoid(b)``, and the
+    decays ``exp(-a_exp[h] * softplus(a_proj + dt_bias))``.  Returns float (q, k, v, beta,
+    decay).  ``conv_state_advance`` moves the slot's rows on afterwards."""
+    _need_cuda(proj, conv_w, a_proj, dt_bias, a_exp, token_req, qo_indptr, slots, state)
+    tokens = proj.shape[0]
+    qk, vv = kv_heads * dim, heads * vdim
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and proj.shape[1] >= 2 * qk + vv + heads
+    assert tuple(conv_w.shape) == (2 * qk + vv, taps) and conv_w.is_contiguous()
+    assert a_proj.dtype == torch.float32 and a_proj.is_contiguous()
+    assert tuple(a_proj.shape) == (tokens, heads * dim)
+    assert dt_bias.dtype == torch.float32 and dt_bias.numel() == heads * dim
+    assert a_exp.dtype == torch.float32 and a_exp.numel() == heads
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    assert state.shape[1] >= gated_delta_state_size(heads, kv_heads, dim, vdim, taps)
+    dev = proj.device
+    q = torch.empty((tokens, qk), dtype=torch.float32, device=dev)
+    k = torch.empty((tokens, qk), dtype=torch.float32, device=dev)
+    v = torch.empty((tokens, vv), dtype=torch.float32, device=dev)
+    beta = torch.empty((tokens, heads), dtype=torch.float32, device=dev)
+    decay = torch.empty((tokens, heads * dim), dtype=torch.float32, device=dev)
+    code = lib.get("gated_delta").mstar_delta_prepare(
+        proj.data_ptr(), proj.stride(0), conv_w.data_ptr(), _dt(conv_w), a_proj.data_ptr(),
+        dt_bias.data_ptr(), a_exp.data_ptr(), token_req.data_ptr(), qo_indptr.data_ptr(),
+        slots.data_ptr(), state.data_ptr(), state.stride(0), q.data_ptr(), k.data_ptr(),
+        v.data_ptr(), beta.data_ptr(), decay.data_ptr(), tokens, heads, kv_heads, dim, vdim, taps,
+        float(unit_eps), _stream())
+    if code == -1:
+        raise KernelError(f"delta-rule input kernel refuses heads={heads}, kv_heads={kv_heads}, "
+                          f"dim={dim}, vdim={vdim}, taps={taps}")
+    check(code, "delta_prepare")
+    return q, k, v, beta, decay
+
+
+def delta_scan(q, k, v, beta, decay, qo_indptr, slots, state: torch.Tensor, entries: int,
+               heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> torch.Tensor:
+    """The gated delta rule over the tokens of ``entries`` batch entries, each continuing the
+    matrix in its slot (updated in place).  Returns float [tokens, heads * vdim]."""
+    _need_cuda(q, k, v, beta, decay, qo_indptr, slots, state)
+    for t in (q, k, v, beta, decay):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    assert state.dtype == torch.float32 and state.dim() == 2 and state.stride(1) == 1
+    tokens = q.shape[0]
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    offset = (taps - 1) * (2 * kv_heads * dim + heads * vdim)
+    code = lib.get("gated_delta").mstar_delta_scan(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+        qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0), offset,
+        out.data_ptr(), entries, heads, kv_heads, dim, vdim, _stream())
+    if code == -1:
+        raise KernelError(f"delta-rule scan refuses heads={heads}, kv_heads={kv_heads}, dim={dim} "
+                          "(dim at most 512)")
+    check(code, "delta_scan")
+    return out
+
+
+def delta_finish(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, heads: int, vdim: int,
+                 eps: float, out_dtype: torch.dtype, scale: float = 1.0) -> torch.Tensor:
+    """o / rms(o per head) * weight * sigmoid(gate) * scale: float ``o`` [tokens, heads * vdim],
+    ``gate`` of the same shape in ``out_dtype``, float ``weight`` [vdim] shared by the heads."""
+    _need_cuda(o, gate, weight)
+    assert o.dtype == torch.float32 and o.is_contiguous()
+    assert weight.dtype == torch.float32 and weight.numel() == vdim
+    assert gate.dtype == out_dtype and gate.stride(1) == 1 and gate.shape == o.shape
+    out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+    check(lib.get("gated_delta").mstar_delta_finish(
+        o.data_ptr(), gate.data_ptr(), gate.stride(0), weight.data_ptr(), out.data_ptr(),
+        _DT[out_dtype], o.shape[0], heads, vdim, float(eps), float(scale), _stream()),
+        "delta_finish")
     return out

@@ -47,6 +47,8 @@ LIBRARIES = {
     "attention_sink": ("cuda", ["attention_sink.cu"], []),
     "attention_sink_tc": ("cuda", ["attention_sink_tc.cu"], []),
     "selective_scan": ("cuda", ["selective_scan.cu"], []),
+    "gated_delta": ("cuda", ["gated_delta.cu"], []),
+    "hyper": ("cuda", ["hyper.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }
 

@@ -36,6 +36,19 @@ _SIGNATURES = {
                                  _vp],
         "mstar_sigmoid_gate_mul": [_vp, _vp, _i, _i, _i, _i, _vp],
         "mstar_head_gate_mul": [_vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _vp],
+        "mstar_bias_act_mul": [_vp, _vp, _i, _vp, _i, _i, _i, _i, _vp],
+    },
+    "hyper": {
+        "mstar_hyper_step": [_vp, _vp, _vp, _vp, _vp, _f, _f, _vp, _vp, _vp, _vp, _vp, _vp, _vp,
+                             _i, _i, _i, _f, _i, _i, _vp],
+        "mstar_weighted_sum2": [_vp, _vp, _vp, _ll, _f, _f, _i, _vp],
+    },
+    "gated_delta": {
+        "mstar_delta_prepare": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp,
+                                _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
+        "mstar_delta_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i,
+                             _i, _vp],
+        "mstar_delta_finish": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
     },
     "matrix_memory": {
         "mstar_matrix_memory_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i,
@@ -58,14 +71,14 @@ _SIGNATURES = {
     "attention_sink": {
         "mstar_sink_prepare": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i,
                                _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _vp, _i, _i, _vp, _vp,
-                               _vp, _ll, _vp],
+                               _vp, _ll, _i, _i, _f, _i, _vp],
         "mstar_conv_state_advance": [_vp, _i, _i, _i, _vp, _vp, _vp, _ll, _i, _vp],
         "mstar_sink_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
-                                         _i, _i, _i, _f, _i, _vp],
+                                         _i, _i, _i, _f, _i, _f, _vp, _vp, _i, _vp],
     },
     "attention_sink_tc": {
         "mstar_sink_attention_tc": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                    _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _vp],
+                                    _i, _i, _i, _i, _f, _i, _vp, _vp, _i, _i, _f, _vp, _vp],
     },
     "selective_scan": {
         "mstar_conv_silu": [_vp, _i, _vp, _vp, _i, _vp, _vp, _vp, _vp, _ll, _vp, _i, _i, _i, _i,

@@ -17,7 +17,11 @@ product in float, a kernel that adds the bias, norms, rotates and fills the cach
 an attention kernel that walks the kept first keys and the window's keys.  The same path
 takes a short causal convolution over time on the q and k channels (its last inputs are
 per-request state in a slot), values that are the keys before their norm, and one sigmoid
-gate a head on the output; the gate's rows ride in the fused first product.
+gate a head on the output; the gate's rows ride in the fused first product.  Further
+options of that path: an RMS norm over the whole q (and k) projection instead of a head,
+rotary pairs of neighbouring features, a query temperature that grows with the logarithm of
+the position, a tanh soft cap on the scores, a sink in the softmax's denominator (a learned
+number a head, or zero), and a sigmoid gate a feature on the heads' outputs.
 """
 from __future__ import annotations
 
@@ -42,6 +46,8 @@ class Attention:
                                                         else spec.value_dim))
         if spec.head_gate:
             kv_rows += spec.num_heads           # the gate's rows come last
+        if spec.feature_gate:
+            kv_rows += spec.num_heads * spec.value_dim
         if spec.shares_kv:
             first = {"q.weight": ParamSpec((q_rows, spec.hidden_size))}
         else:
@@ -49,8 +55,11 @@ class Attention:
             if spec.bias:
                 first["qkv.bias"] = ParamSpec((q_rows + kv_rows,), role="vector", init="zeros")
         if spec.qk_norm_eps is not None:
-            first["q_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
-            first["k_norm.weight"] = ParamSpec((spec.head_dim,), role="vector", init="ones")
+            per_q, per_k = (spec.num_heads, spec.num_kv_heads) if spec.qk_norm_whole else (1, 1)
+            first["q_norm.weight"] = ParamSpec((per_q * spec.head_dim,), role="vector", init="ones")
+            first["k_norm.weight"] = ParamSpec((per_k * spec.head_dim,), role="vector", init="ones")
+        if spec.sink == "learned":
+            first["sink"] = ParamSpec((spec.num_heads,), role="vector", init="zeros")
         if spec.conv_taps:
             first["q_conv.weight"] = ParamSpec((q_rows, spec.conv_taps), role="vector")
             first["k_conv.weight"] = ParamSpec((spec.num_kv_heads * spec.head_dim, spec.conv_taps),
@@ -89,6 +98,18 @@ class Attention:
             raise ValueError("values that are the keys have the keys' size")
         if spec.conv_taps and spec.bias:
             raise ValueError("a convolution on biased projections is not defined here")
+        if spec.head_gate and spec.feature_gate:
+            raise ValueError("an attention has a gate a head or a gate a feature, not both")
+        if spec.qk_norm_whole and (spec.conv_taps or spec.qk_norm_eps is None):
+            raise ValueError("a norm over the whole projection needs qk_norm_eps and no "
+                             "convolution")
+        if spec.sink not in (None, "learned", "zero"):
+            raise ValueError(f"sink {spec.sink!r} is not known (learned, zero)")
+        self.sink = None
+        if spec.sink == "learned":
+            self.sink = params["sink"].float().contiguous()
+        elif spec.sink == "zero":
+            self.sink = torch.zeros(spec.num_heads, dtype=torch.float32, device=runtime.device)
         small = [w for w in (self.bias, self.q_norm, self.k_norm, self.q_conv, self.k_conv)
                  if w is not None]
         if len({w.dtype for w in small}) > 1:   # the input kernel takes them in one type
@@ -99,9 +120,11 @@ class Attention:
             from .rope import rope_inverse_frequencies
 
             p = spec.position
-            if p.kind not in ("rope", "none") or p.interleaved:
-                raise ValueError("this attention rotates split-half pairs (a rope position spec "
-                                 "without interleaving) or nothing")
+            if p.kind not in ("rope", "none"):
+                raise ValueError("this attention rotates pairs of features (a rope position "
+                                 "spec) or nothing")
+            if p.interleaved and p.scaling is not None:
+                raise ValueError("frequency scaling goes with split-half pairs here")
             self.rot = p.rotary_dim if p.kind == "rope" else 0
             self.freq = None
             if self.rot:
@@ -140,15 +163,20 @@ class Attention:
                              ctx.cache_pos, ctx.token_req, cache.block_table, cache.kv,
                              s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim, self.rot,
                              cache.page_size, s.qk_norm_eps or 0.0, self.runtime.dtype,
-                             conv=conv, value_from_key=s.value_from_key)
+                             conv=conv, value_from_key=s.value_from_key,
+                             interleaved=s.position.interleaved and self.rot > 0,
+                             norm_whole=s.qk_norm_whole, q_temp=s.q_temp)
         if s.conv_taps > 1:
             ops.conv_state_advance(qkv, (s.num_heads + s.num_kv_heads) * s.head_dim, s.conv_taps,
                                    ctx.qo_indptr, ctx.slots, cache.state, ctx.num_entries)
         gate = qkv[:, qkv.shape[1] - s.num_heads:] if s.head_gate else None
+        if s.feature_gate:
+            gate = qkv[:, qkv.shape[1] - s.num_heads * s.value_dim:]
         out = ops.sink_attention(q, cache.kv, cache.block_table, ctx.token_req, ctx.cache_pos,
                                  s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
                                  cache.page_size, s.window or 0, s.keep_first if s.window else 0,
-                                 self.scale, ctx=ctx, gate=gate)
+                                 self.scale, ctx=ctx, gate=gate, softcap=s.softcap,
+                                 sink=self.sink)
         return ops.linear(out, self.w_out, static_weights=True)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:

@@ -103,6 +103,17 @@ class ResidualStream:
         self.delta: Optional[torch.Tensor] = None
         self.post = None
         self.post_scale = 1.0
+        # set by a block that keeps the residual as several copies (hyper-connections): an
+        # object with ``gather(rows)``; ``h`` is then no longer the residual
+        self.copies = None
+
+    def gather(self, rows: torch.Tensor) -> torch.Tensor:
+        """The float residual of the rows asked for, everything pending added."""
+        from .. import ops
+
+        if self.copies is not None:
+            return self.copies.gather(rows)
+        return ops.gather_add_rows(self.h, self.take_delta(), rows)
 
     def push(self, delta: torch.Tensor, post=None, scale: float = 1.0) -> None:
         if self.delta is not None:

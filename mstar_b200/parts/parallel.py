@@ -1,4 +1,6 @@
-"""Parallel mixer: several mixers side by side on the same input.  The result is the mean of
+"""Parallel mixer: several mixers side by side on the same input.  With ``merge``
+"weighted_sum" the result is ``sum_b scales[b] * branch_b``, handed on uncomputed
+(``ops.WeightedSum``) for the block's kernel to add.  Otherwise the result is the mean of
 their outputs, each divided by its root mean square over the model width and scaled by a
 weight of its own; the mean is float.  The mixer hands it on uncomputed (``ops.MeanOfNorms``):
 the norm that adds it to the residual does both in one kernel, or computes it first.  At most one branch may keep keys and values in pages
@@ -33,7 +35,8 @@ class ParallelMixer:
         for b, branch in enumerate(spec.branches):
             for local, ps in part_class("mixer", branch).param_specs(branch).items():
                 out[f"branch{b}.{local}"] = ps
-            out[f"out{b}.weight"] = ParamSpec((spec.hidden_size,), role="vector", init="ones")
+            if spec.merge == "mean_of_norms":
+                out[f"out{b}.weight"] = ParamSpec((spec.hidden_size,), role="vector", init="ones")
         return out
 
     @classmethod
@@ -60,8 +63,13 @@ class ParallelMixer:
         self.runtime = runtime
         self.branches = [build_part("mixer", branch, _sub(params, f"branch{b}"), runtime)
                          for b, branch in enumerate(spec.branches)]
+        if spec.merge not in ("mean_of_norms", "weighted_sum"):
+            raise ValueError(f"a parallel mixer merges by mean_of_norms or weighted_sum, not "
+                             f"{spec.merge!r}")
+        if spec.merge == "weighted_sum" and len(spec.scales) != len(spec.branches):
+            raise ValueError("a weighted sum needs one scale per branch")
         self.weights = [params[f"out{b}.weight"].float().contiguous()
-                        for b in range(len(spec.branches))]
+                        for b in range(len(spec.branches))] if spec.merge == "mean_of_norms" else []
         self.graph_safe = all(getattr(p, "graph_safe", False) is True for p in self.branches)
         self.side_streams = None
         if len(self.branches) > 1 and os.environ.get("MSTAR_PARALLEL_STREAMS") != "0":
@@ -71,7 +79,7 @@ class ParallelMixer:
     def forward(self, x, ctx: StepContext, cache: LayerCache):
         if self.side_streams is None:
             outs = [branch.forward(x, ctx, cache) for branch in self.branches]
-            return ops.MeanOfNorms(outs, self.weights, self.spec.norm_eps)
+            return self._merge(outs)
         main = torch.cuda.current_stream(self.runtime.device)
         outs = [None] * len(self.branches)
         for b, side in enumerate(self.side_streams, start=1):
@@ -84,7 +92,12 @@ class ParallelMixer:
         # what the side streams allocated is used on the step's stream from here on
         for out in outs[1:]:
             out.record_stream(main)
-        # (left to the norm that adds it to the residual: one kernel for both where it can)
+        return self._merge(outs)
+
+    def _merge(self, outs):
+        # (left to the kernel that adds it to the residual: one kernel for both where it can)
+        if self.spec.merge == "weighted_sum":
+            return ops.WeightedSum(outs, self.spec.scales)
         return ops.MeanOfNorms(outs, self.weights, self.spec.norm_eps)
 
 

@@ -70,5 +70,6 @@ def _builtin() -> None:
     if _done:
         return
     _done = True
-    from . import (attention, block, embedding, latent_attention, matrix_memory, mlp, norm,  # noqa: F401
-                   parallel, rope, routed_experts, selective_scan)   # (they register themselves)
+    from . import (attention, block, embedding, gated_delta, latent_attention,  # noqa: F401
+                   matrix_memory, mlp, norm, parallel, rope, routed_experts,
+                   selective_scan)   # (they register themselves)

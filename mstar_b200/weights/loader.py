@@ -123,6 +123,22 @@ def _target_dtype(spec: ParamSpec, stored: list, dtype: torch.dtype) -> torch.dt
     return dtype
 
 
+def checkpoint_shapes(source):
+    """A function from a checkpoint tensor's name to its shape (None when absent), for
+    configurations that leave a size to the tensors.  Nothing but headers is read."""
+    ckpt = None
+
+    def shape_of(name: str):
+        nonlocal ckpt
+        if ckpt is None:
+            ckpt = _Checkpoint(source)
+        if name not in ckpt.names():
+            return None
+        return ckpt.shape_dtype(name)[0]
+
+    return shape_of
+
+
 def load_parameters(source, param_specs: Mapping[str, ParamSpec],
                     cmap: CheckpointMap, dtype: torch.dtype,
                     device: torch.device | str) -> dict:
