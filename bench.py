@@ -5,7 +5,7 @@ one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--rounds R] [--page-size P]
                     [--impl ours|reference] [--workloads all|none|mixed64|long8]
-    python bench.py --arch tifosun|vudivik [--arch-size small|medium]   (another architecture)
+    python bench.py --arch tifosun|vudivik|relurax|mokotar [--arch-size small|medium]   (another architecture)
 
 One JSON line on stdout.  ``value``: decoded tokens per second of the engine's step
 function plus greedy sampling, timed on the device with CUDA events: W warm-up steps, then
@@ -424,6 +424,8 @@ def arch_bench(args) -> int:
         return vudivik_bench(args)
     if args.arch == "relurax":
         return relurax_bench(args)
+    if args.arch == "mokotar":
+        return mokotar_bench(args)
     pk = peaks()
     t_cfg, l_cfg = tifosun_sizes(args.arch_size)
     page, batch = args.page_size, args.batch
@@ -962,6 +964,255 @@ def relurax_bench(args) -> int:
     return 0
 
 
+def mokotar_sizes(name: str) -> tuple:
+    """(Mokotar config, Vudivik config, Llama config) at layer sizes that resemble a real
+    model's: the four layer kinds in turn (an attention with soft cap, temperature and sink; one
+    normed over the whole projection with rotary pairs; an attention beside a gated delta
+    rule; the first kind again), two copies of the residual, biased gated feed-forwards.  The
+    Vudivik beside it, the closest decoder of this engine (an attention of the same kernel
+    family beside a recurrent scan in every layer), and the Llama have the same width, depth,
+    vocabulary, heads and key/value heads."""
+    if name == "small":
+        width, depth, vocab, ff = 1024, 8, 32000, 2816
+        heads, kv_heads, rank = 8, 2, 64
+    elif name == "medium":
+        width, depth, vocab, ff = 2048, 12, 64000, 5632
+        heads, kv_heads, rank = 16, 4, 128
+    else:
+        raise ValueError(f"unknown size {name!r} (small, medium)")
+    base = dict(heads=heads, kv_heads=kv_heads, dim=128, vdim=128, scale=128 ** -0.5)
+    att = dict(base, q_temp={"coef": 0.3, "every": 512}, softcap=30.0)
+    att2 = dict(base, rot={"base": 500000.0, "dims": 64})
+    par = {"left": dict(base, rot={"base": 500000.0, "dims": 64}),
+           "right": dict(heads=heads, kv_heads=heads, dim=128, vdim=128, conv=4, decay_rank=rank,
+                         gate_rank=rank),
+           "left_scale": 1.0, "right_scale": 1.0}
+    kinds = [("attention", att), ("attention_2", att2), ("parallel", par), ("attention", att)]
+    layers = [{"type": kinds[i % 4][0], "mixer": json.loads(json.dumps(kinds[i % 4][1])),
+               "mlp": {"kind": "dense", "ff": ff}} for i in range(depth)]
+    mokotar = {"architecture": "Mokotar", "width": width, "vocab": vocab, "norm": {"eps": 1e-6},
+               "residual_mult": 0.5, "streams": 2, "layers": layers}
+    vudivik, _ = vudivik_sizes(name)
+    llama = dict(ORPHEUS_3B, num_hidden_layers=depth, hidden_size=width,
+                 num_attention_heads=heads, num_key_value_heads=kv_heads, head_dim=128,
+                 intermediate_size=ff, vocab_size=vocab, tie_word_embeddings=False)
+    return mokotar, vudivik, llama
+
+
+def mokotar_bench(args) -> int:
+    """``--arch mokotar``: prefill and decode throughput of the Mokotar decoder (random
+    weights, bfloat16) beside the Vudivik and Llama decoders at equal size, through the same
+    step function; then its kernels alone at the sizes of one layer, each beside the like
+    kernel of the closest decoder (attention with sink, soft cap and feature gate: Vudivik's
+    window attention and the Llama attention; its input kernel: Vudivik's; the delta rule:
+    Vudivik's selective scan and the matrix-memory scan; the hyper-connection kernel: the
+    fused post-norm, add and norm), with what each has to move against the measured peaks.
+    One JSON line."""
+    import torch
+
+    from mstar_b200 import ops
+    from mstar_b200.parts.base import StepContext
+
+    pk = peaks()
+    m_cfg, v_cfg, l_cfg = mokotar_sizes(args.arch_size)
+    page, batch = args.page_size, args.batch
+    out = {"arch": "Mokotar", "size": args.arch_size, "batch": batch, "prompt_len": PROMPT_LEN,
+           "peaks": pk["source"], "models": {}, "kernels": {}}
+    _time_models(args, (("mokotar", m_cfg), ("vudivik", v_cfg), ("llama", l_cfg)), out)
+
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=g, device=dev)).to(torch.bfloat16)
+
+    def i32(v):
+        return torch.tensor(v, dtype=torch.int32, device=dev)
+
+    def record(name, ms, nbytes=None, flops=None, **more):
+        row = {"ms": round(ms, 4)}
+        if nbytes is not None:
+            row["gbs"] = round(nbytes / ms / 1e6, 1)
+            row["frac_hbm"] = round(nbytes / ms / 1e6 / pk["hbm_gbs"], 4)
+        if flops is not None:
+            row["tflops"] = round(flops / ms / 1e9, 2)
+            row["frac_bf16"] = round(flops / ms / 1e9 / pk["bf16_tflops"], 5)
+        row.update(more)
+        out["kernels"][name] = row
+
+    width = m_cfg["width"]
+    att = m_cfg["layers"][0]["mixer"]
+    par = m_cfg["layers"][2]["mixer"]
+    H, G, hd = att["heads"], att["kv_heads"], att["dim"]
+    ctx_len = PROMPT_LEN
+    pages_per = -(-ctx_len // page)
+    for tokens, reqs, label in ((batch, batch, "decode"), (PROMPT_LEN, 1, "prefill")):
+        per = tokens // reqs
+        copies = 1 if label == "prefill" else max(1, -(-(160 << 20) // (reqs * ctx_len * G * hd * 4)))
+        caches = [rnd(reqs * pages_per + 1, 2, G, page, hd) for _ in range(copies)]
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        token_req = i32([r for r in range(reqs) for _ in range(per)])
+        cache_pos = i32([ctx_len - per + k for _ in range(reqs) for k in range(per)])
+        indptr = i32([k * per for k in range(reqs + 1)])
+        kv_len = i32([ctx_len] * reqs)
+        slots = i32(list(range(reqs)))
+        q = rnd(tokens, H * hd)
+        sc = StepContext(num_tokens=tokens, num_entries=reqs, token_req=token_req,
+                         positions=cache_pos, cache_pos=cache_pos, qo_indptr=indptr, kv_len=kv_len,
+                         slots=slots, q_lens=[per] * reqs, kv_lens=[ctx_len] * reqs,
+                         host_slots=list(range(reqs)), max_q_len=per, max_kv_len=ctx_len,
+                         num_decode=reqs if per == 1 else 0)
+        turn = {"i": 0}
+        rows = (H + 2 * G) * hd
+        qkv = torch.randn(tokens, rows + H * hd, device=dev)     # [q | k | v | gate]
+        sink = torch.randn(H, device=dev)
+        keys = sum(ctx_len - per + k + 1 for k in range(per)) * reqs
+        all_bytes = reqs * ctx_len * G * hd * 4.0
+
+        def attend(form):
+            c = caches[turn["i"] % copies].view(reqs * pages_per + 1, -1)
+            turn["i"] += 1
+            if form == "mokotar":       # every key, soft cap, sink, a gate a feature
+                return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, 0,
+                                          0, att["scale"], ctx=sc, gate=qkv[:, rows:],
+                                          softcap=att["softcap"], sink=sink)
+            if form == "plain":         # the same kernel without the three options
+                return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, 0,
+                                          0, att["scale"], ctx=sc)
+            return ops.sink_attention(q, c, table, token_req, cache_pos, H, G, hd, hd, page, 1024,
+                                      4, att["scale"], ctx=sc)
+
+        reps = max(copies, 4) if label == "decode" else 2
+        ms = _time_graph(lambda: attend("mokotar"), reps=reps)
+        record(f"sink_attention_{label}", ms, nbytes=all_bytes, flops=4.0 * H * keys * hd)
+        ms = _time_graph(lambda: attend("plain"), reps=reps)
+        record(f"same_kernel_without_cap_sink_gate_{label}", ms, nbytes=all_bytes,
+               flops=4.0 * H * keys * hd)
+        seen = min(ctx_len, 1024 + per)
+        wkeys = sum(min(ctx_len - per + k + 1, 1024) + 4 for k in range(per)) * reqs
+        ms = _time_graph(lambda: attend("vudivik"), reps=reps)
+        record(f"vudivik_window_attention_{label}", ms, nbytes=reqs * (seen + 4) * G * hd * 4.0,
+               flops=4.0 * H * wkeys * hd)
+        out_l = torch.empty(tokens, H * hd, dtype=torch.bfloat16, device=dev)
+        turn["i"] = 0
+        if label == "decode":
+            def llama_attend():
+                c = caches[turn["i"] % copies]
+                turn["i"] += 1
+                ops.paged_decode_attention(q, q.stride(0), out_l, c, table, token_req, cache_pos,
+                                           tokens, H, G, hd, page, 0, att["scale"], ctx_len)
+        else:
+            def llama_attend():
+                ops.paged_prefill_attention(q, q.stride(0), out_l, caches[0], table, indptr, kv_len,
+                                            0, reqs, per, H, G, hd, page, 0, att["scale"])
+        ms = _time_graph(llama_attend, reps=reps)
+        record(f"llama_attention_{label}", ms, nbytes=all_bytes, flops=4.0 * H * keys * hd)
+        # the input kernels: head norm + temperature; whole-projection norm + rotary pairs;
+        # beside Vudivik's bias + head norm + split-half rotation
+        c0 = caches[0].view(reqs * pages_per + 1, -1)
+        nq, nk = rnd(hd), rnd(hd)
+        nqw, nkw = rnd(H * hd), rnd(G * hd)
+        freq = torch.rand(32, dtype=torch.float64, device=dev)
+        io_bytes = tokens * (rows * 4 + H * hd * 2 + 2 * G * hd * 2.0)
+        ms = _time_graph(lambda: ops.sink_prepare(
+            qkv, None, nq, nk, None, cache_pos, cache_pos, token_req, table, c0, H, G, hd, hd, 0,
+            page, 1e-6, torch.bfloat16, q_temp=(0.3, 512)), reps=8)
+        record(f"norm_temperature_cache_{label}", ms, nbytes=io_bytes)
+        ms = _time_graph(lambda: ops.sink_prepare(
+            qkv, None, nqw, nkw, freq, cache_pos, cache_pos, token_req, table, c0, H, G, hd, hd, 64,
+            page, 1e-6, torch.bfloat16, interleaved=True, norm_whole=True), reps=8)
+        record(f"whole_norm_rope_pairs_cache_{label}", ms, nbytes=io_bytes)
+        bias = rnd(rows)
+        freq_v = torch.rand(hd // 2, dtype=torch.float64, device=dev)
+        ms = _time_graph(lambda: ops.sink_prepare(
+            qkv, bias, nq, nk, freq_v, cache_pos, cache_pos, token_req, table, c0, H, G, hd, hd, hd,
+            page, 1e-6, torch.bfloat16), reps=8)
+        record(f"vudivik_bias_norm_rope_cache_{label}", ms, nbytes=io_bytes)
+
+        # the gated delta rule of one layer
+        r = par["right"]
+        DH, DG, D, VD, taps = r["heads"], r["kv_heads"], r["dim"], r["vdim"], r["conv"]
+        channels = 2 * DG * D + DH * VD
+        size = ops.gated_delta_state_size(DH, DG, D, VD, taps)
+        n_state = max(1, -(-(160 << 20) // (reqs * size * 4))) if label == "decode" else 1
+        states = [torch.zeros(reqs, size, device=dev) for _ in range(n_state)]
+        proj = torch.randn(tokens, channels + DH + 2 * r["decay_rank"], device=dev)
+        conv_w = rnd(channels, taps)
+        a_proj = torch.randn(tokens, DH * D, device=dev)
+        dt_bias, a_exp = torch.randn(DH * D, device=dev) - 4.0, torch.rand(DH, device=dev) + 0.5
+        pre = ops.delta_prepare(proj, conv_w, a_proj, dt_bias, a_exp, token_req, indptr, slots,
+                                states[0], DH, DG, D, VD, taps, 1e-6)
+        ms = _time_graph(lambda: ops.delta_prepare(proj, conv_w, a_proj, dt_bias, a_exp, token_req,
+                                                   indptr, slots, states[0], DH, DG, D, VD, taps,
+                                                   1e-6), reps=8)
+        record(f"delta_conv_unit_decay_{label}", ms,
+               nbytes=tokens * ((channels + DH + DH * D) * 4 + (channels + DH + DH * D) * 4.0))
+        turn["i"] = 0
+
+        def scan():
+            st = states[turn["i"] % n_state]
+            turn["i"] += 1
+            return ops.delta_scan(*pre, indptr, slots, st, reqs, DH, DG, D, VD, taps)
+
+        ms = _time_graph(scan, reps=max(n_state, 4) if label == "decode" else 2)
+        record(f"delta_scan_{label}", ms, nbytes=reqs * DH * D * VD * 8.0,
+               tokens_per_us=round(per / ms / 1e3, 3))
+        o = torch.randn(tokens, DH * VD, device=dev)
+        gate, nw = rnd(tokens, DH * VD), torch.randn(VD, device=dev)
+        ms = _time_graph(lambda: ops.delta_finish(o, gate, nw, DH, VD, 1e-6, torch.bfloat16), reps=8)
+        record(f"delta_head_norm_gate_{label}", ms, nbytes=tokens * DH * VD * 8.0)
+        # Vudivik's recurrent branch at its sizes: convolution and scan
+        vr = v_cfg["layers"][0]["mixer"]["right"]
+        inner, n_st, rank, vt = vr["inner"], vr["state"], vr["dt_rank"], vr["conv"]
+        vsize = ops.selective_scan_state_size(inner, n_st, vt)
+        vstate = torch.zeros(reqs, vsize, device=dev)
+        xz = rnd(tokens, 2 * inner)
+        cw, cb = rnd(inner, vt), rnd(inner)
+        xc = ops.conv_silu(xz, cw, cb, token_req, indptr, slots, vstate, inner, vt,
+                           weight_t=cw.float().t().contiguous(), bias_f32=cb.float())
+        ms = _time_graph(lambda: ops.conv_silu(xz, cw, cb, token_req, indptr, slots, vstate, inner,
+                                               vt, weight_t=cw.float().t().contiguous(),
+                                               bias_f32=cb.float()), reps=8)
+        record(f"vudivik_conv_silu_{label}", ms, nbytes=tokens * inner * 4.0)
+        vproj = torch.randn(tokens, rank + 2 * n_st, device=dev)
+        w_dt, b_dt = torch.randn(inner, rank, device=dev) * 0.1, torch.randn(inner, device=dev) - 4.0
+        a_neg, d_skip = -torch.rand(inner, n_st, device=dev) - 0.5, torch.ones(inner, device=dev)
+        ms = _time_graph(lambda: ops.selective_scan(xc, xz, vproj, w_dt, b_dt, a_neg, d_skip, indptr,
+                                                    slots, vstate, reqs, inner, n_st, rank, vt,
+                                                    max_q_len=per), reps=4 if label == "decode" else 2)
+        record(f"vudivik_selective_scan_{label}", ms, nbytes=reqs * inner * n_st * 8.0,
+               tokens_per_us=round(per / ms / 1e3, 3))
+
+    # between the sublayers: write of the copies, read and norm; beside the fused post-norm,
+    # add and norm of the sandwich blocks; the biased gate beside the plain one
+    ff = m_cfg["layers"][0]["mlp"]["ff"]
+    S = m_cfg["streams"]
+    for tokens, label in ((batch, "decode"), (PROMPT_LEN, "prefill")):
+        x = torch.randn(tokens, S, width, device=dev)
+        y1, y2, w = rnd(tokens, width), rnd(tokens, width), rnd(width)
+        mix = torch.eye(S, device=dev).contiguous()
+        t_out, t_in = torch.ones(S, device=dev), torch.full((S,), 1.0 / S, device=dev)
+        ms = _time_graph(lambda: ops.hyper_step(x, y=y1, y2=y2, mix=mix, out=t_out, read=t_in,
+                                                norm_weight=w, eps=1e-6, out_dtype=torch.bfloat16),
+                         reps=20)
+        record(f"hyper_write_read_norm_{label}", ms, nbytes=tokens * width * (8.0 * S + 2 + 2 + 2))
+        resid = torch.randn(tokens, width, device=dev)
+        wb = torch.randn(width, device=dev)
+        ms = _time_graph(lambda: ops.add_postnorm_rmsnorm(resid, y1, wb, 1e-5, 0.0, w, 1e-5, 0.0,
+                                                          torch.bfloat16), reps=20)
+        record(f"postnorm_add_norm_{label}", ms, nbytes=tokens * width * (4 + 4 + 2 + 2.0))
+        gu = torch.randn(tokens, 2 * ff, device=dev)
+        bias = rnd(2 * ff)
+        ms = _time_graph(lambda: ops.bias_act_mul(gu, bias, torch.bfloat16), reps=20)
+        record(f"bias_silu_mul_{label}", ms, nbytes=tokens * ff * (8.0 + 2))
+        gub = rnd(tokens, 2 * ff)
+        ms = _time_graph(lambda: ops.silu_mul(gub), reps=20)
+        record(f"silu_mul_{label}", ms, nbytes=tokens * ff * (4.0 + 2))
+    ops.check_error_word(dev)
+    print(json.dumps(out))
+    return 0
+
+
 # --------------------------------------------------------------- single kernels
 def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
     """Median milliseconds of one call of ``fn`` when ``reps`` calls are replayed as one
@@ -1205,7 +1456,7 @@ def main() -> int:
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),
                     help="layer sizes; the default is the benchmark model")
-    ap.add_argument("--arch", default=None, choices=["tifosun", "vudivik", "relurax"],
+    ap.add_argument("--arch", default=None, choices=["tifosun", "vudivik", "relurax", "mokotar"],
                     help="measure another architecture beside the Llama decoder at equal size "
                          "(prefill, decode, its own kernels) instead of the headline workload")
     ap.add_argument("--arch-size", default="small", choices=["small", "medium"])

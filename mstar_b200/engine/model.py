@@ -148,8 +148,9 @@ def load_model(source, dtype="bfloat16", device="cuda:0", *, config: Optional[Mo
     # sizes that the configuration leaves to the tensors' shapes
     from ..weights.loader import checkpoint_shapes
 
-    config = config.with_shapes(checkpoint_shapes(tensors if tensors is not None
-                                                  else Path(source)))
+    if hasattr(config, "with_shapes"):
+        config = config.with_shapes(checkpoint_shapes(tensors if tensors is not None
+                                                      else Path(source)))
     layout = config.layout()
     arch = get_architecture(config.architecture)
     specs = model_param_specs(layout)

@@ -212,7 +212,7 @@ class HyperBlock:
             for q in (1, 2) if spec.ffn is not None else (1,):
                 out[f"hc{q}.in"] = ParamSpec((s,), role="vector", init="ones")
                 out[f"hc{q}.out"] = ParamSpec((s,), role="vector", init="ones")
-                out[f"hc{q}.mix"] = ParamSpec((s, s), role="vector", init="ones")
+                out[f"hc{q}.mix"] = ParamSpec((s, s), role="vector", init="identity")
         return out
 
     @classmethod

@@ -21,7 +21,8 @@ class ParamSpec:
     role: "matrix" (GEMM weight), "table" (embedding), "vector" (norm weight and
     other small float tensors), "int_table" (integer lookup tables, kept int32).
     ``init``: how random-weights mode draws it: "normal" (std from the caller),
-    "ones" (norm weights: 1, or 1 + noise when the caller asks for it), "zeros".
+    "ones" (norm weights: 1, or 1 + noise when the caller asks for it), "zeros",
+    "identity" (a square mixing table).
     """
 
     shape: tuple

@@ -60,6 +60,8 @@ def random_checkpoint(config: ModelConfig, seed: int, *, std: float = 0.02,
             store = vector_dtype or dtype
         elif spec.init == "zeros":
             t = torch.zeros(shape, dtype=torch.float32, device=device)
+        elif spec.init == "identity":
+            t = torch.eye(shape[0], shape[1], dtype=torch.float32, device=device)
         else:
             t = std * torch.randn(shape, generator=gen, device=device, dtype=torch.float32)
         out[name] = t.to(torch.bfloat16).to(store)
