@@ -1152,7 +1152,7 @@ def mokotar_bench(args) -> int:
         def scan():
             st = states[turn["i"] % n_state]
             turn["i"] += 1
-            return ops.delta_scan(*pre, indptr, slots, st, reqs, DH, DG, D, VD, taps)
+            return ops.delta_scan(*pre, indptr, slots, st, reqs, DH, DG, D, VD, taps, max_q_len=per)
 
         ms = _time_graph(scan, reps=max(n_state, 4) if label == "decode" else 2)
         record(f"delta_scan_{label}", ms, nbytes=reqs * DH * D * VD * 8.0,

@@ -42,6 +42,7 @@ struct SinkTcArgs {
     int gate_stride;
     int gate_features;
     float scale, softcap;       // softcap 0: none
+    float cap_in, cap_log2e;    // 2 log2(e) scale / softcap and softcap log2(e)
     const float* sink;          // null, or one number a query head
 };
 
@@ -206,8 +207,10 @@ sink_attention_tc_kernel(SinkTcArgs a) {
                     const bool ok = v < visible && key <= cp && (cp - key < W || key < a.keep_first);
                     float sv = -INFINITY;
                     if (ok) {
+                        // cap * tanh(x / cap) * log2(e) with tanh(z) = 1 - 2 / (2^(2 z log2 e) + 1):
+                        // one exponential and one division, exact at both ends
                         sv = a.softcap > 0.f
-                                 ? a.softcap * tanhf(s[j][q4] * a.scale / a.softcap) * 1.4426950408889634f
+                                 ? a.cap_log2e * (1.f - __fdividef(2.f, exp2f(s[j][q4] * a.cap_in) + 1.f))
                                  : s[j][q4] * a.scale_log2e;
                     }
                     s[j][q4] = sv;
@@ -401,8 +404,18 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
     const float w_a = exp2f(m_a - M), w_b = exp2f(m_b - M);   // 0 for a split that saw no key
     const float L = (warp_sum(l_a * w_a + l_b * w_b) + st_sink_term(sink, row % nq, M)) /
                     (gate_features ? 1.f : st_head_gate(gate, gate_stride, row / nq, row % nq));
-    for (int d0 = 0; d0 < vd; d0 += 32) {
-        const int d = d0 + lane;
+    // a gate a feature: all of a lane's gate values are asked for before the sums (vd <= 256)
+    float gv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = i * 32 + lane;
+        gv[i] = (gate_features && d < vd)
+                    ? gate[(size_t)(row / nq) * gate_stride + (size_t)(row % nq) * vd + d] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = i * 32 + lane;
+        if (i * 32 >= vd) break;
         float sum = 0.f;
 #pragma unroll 8
         for (int s = 0; s < splits; ++s) {
@@ -410,8 +423,8 @@ __global__ void sink_merge_kernel(const float* __restrict__ scratch, bf16* __res
             if (d < vd) sum = fmaf(base[(size_t)s * (vd + 2) + d], w, sum);
         }
         if (d < vd)
-            out[(size_t)row * vd + d] = __float2bfloat16_rn(
-                sum / L * (gate_features ? st_gate(gate, gate_stride, 1, vd, row / nq, row % nq, d) : 1.f));
+            out[(size_t)row * vd + d] =
+                __float2bfloat16_rn(sum / L * (gate_features ? 1.f / (1.f + expf(-gv[i])) : 1.f));
     }
 }
 
@@ -487,6 +500,8 @@ MSTAR_API int mstar_sink_attention_tc(const void* q, int q_stride, void* out, co
     a.gate_features = gate != nullptr && gate_features;
     a.scale = scale;
     a.softcap = softcap;
+    a.cap_in = softcap > 0.f ? 2.f * 1.4426950408889634f * scale / softcap : 0.f;
+    a.cap_log2e = softcap * 1.4426950408889634f;
     a.sink = sink;
     cudaStream_t s = (cudaStream_t)stream;
     const int wide = hd > vd ? hd : vd;

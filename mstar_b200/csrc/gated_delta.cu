@@ -16,6 +16,7 @@
 // A slot is [(taps - 1) * (2 G D + H VD) convolution inputs | S^T as [H][VD][D]], float.
 // Everything here is float whatever the activation type.
 #include "common.cuh"
+#include "mma_util.cuh"
 
 // ------------------------------------------------------------------ prepare
 struct DeltaPrepArgs {
@@ -129,8 +130,9 @@ MSTAR_API int mstar_delta_prepare(const float* proj, int row_stride, const void*
 }
 
 // ------------------------------------------------------------------ scan
-#define GD_THREADS 128
+#define GD_THREADS 256
 #define GD_ROWS 16          // most rows of a column that one lane keeps
+#define GD_CHUNK 16         // tokens staged at a time
 
 struct DeltaScanArgs {
     const float* q;
@@ -147,19 +149,38 @@ struct DeltaScanArgs {
     int H, G, D, VD, chunk;
 };
 
+__device__ __forceinline__ void gd_copy4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+__device__ __forceinline__ void gd_copy16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(
+                     (uint32_t)__cvta_generic_to_shared(dst)), "l"(src));
+}
+
 // A block owns GD_THREADS / L value columns of one head of one batch entry; the D rows of a
-// column lie on L lanes, lane l keeping rows l, l + L, ...  The token's q, k and decay rows
-// (shared by the block's columns) are staged in shared memory, `chunk` tokens at a time.
-template <int L>
+// column lie on L lanes, lane l keeping rows l, l + L, ...  What the block's columns share of
+// a token (its q, k and decay rows, its write strength) and their values are staged in shared
+// memory, `chunk` tokens at a time, the next chunk on its way (cp.async) while this one is
+// walked.  Along the chain a token costs the decay, four short sums, the shuffles over the L
+// lanes and the write; q . k does not depend on the state and runs beside it.
+// A warp that waits for its own shuffles has nothing else to issue, so a token's time is the
+// length of its instruction chain: the lanes of a column are as many as leave four rows a lane
+// (a whole warp a column from 128 rows on), R is the compiled number of rows a lane.
+// VEC: rows are whole 16-byte pieces (D a multiple of 4).
+template <int L, int R, bool VEC>
 __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a) {
-    extern __shared__ float stage[];          // [chunk][3][D]: q, k, decay
+    extern __shared__ __align__(16) float stage[];     // [2][chunk][3 D + COLS + 4]
     constexpr int COLS = GD_THREADS / L;
     const int e = blockIdx.x, h = blockIdx.y;
     const int g = h / (a.H / a.G);
     const int lane = threadIdx.x % L;
-    const int col = blockIdx.z * COLS + threadIdx.x / L;
+    const int mycol = threadIdx.x / L;
+    const int col0 = blockIdx.z * COLS;
+    const int col = col0 + mycol;
     const bool live = col < a.VD;
     const int D = a.D;
+    const int per_tok = 3 * D + COLS + 4;              // q, k, decay, values, beta (+ padding)
     const unsigned long long waited = pdl_wait();
     const float* q = pdl_after(a.q, waited);
     const float* k = pdl_after(a.k, waited);
@@ -169,62 +190,100 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
     float* state = pdl_after(a.state, waited);
     const int start = a.qo_indptr[e], n = a.qo_indptr[e + 1] - start;
     if (n <= 0) return;
+    const int qk = a.G * D, hd = a.H * D, vv = a.H * a.VD;
+    const int ncols = min(COLS, a.VD - col0);
+
+    auto fetch = [&](int buf, int base) {
+        const int here = min(a.chunk, n - base);
+        float* dst0 = stage + (size_t)buf * a.chunk * per_tok;
+        if constexpr (VEC) {
+            const int pieces = D / 4;
+            for (int i = threadIdx.x; i < here * 3 * pieces; i += GD_THREADS) {
+                const int j = i / (3 * pieces), r = i - j * 3 * pieces;
+                const int which = r / pieces, d = (r - which * pieces) * 4;
+                const size_t tok = (size_t)(start + base + j);
+                const float* src = which == 0 ? q + tok * qk + (size_t)g * D + d
+                                 : which == 1 ? k + tok * qk + (size_t)g * D + d
+                                              : decay + tok * hd + (size_t)h * D + d;
+                gd_copy16(dst0 + (size_t)j * per_tok + which * D + d, src);
+            }
+        } else {
+            for (int i = threadIdx.x; i < here * 3 * D; i += GD_THREADS) {
+                const int j = i / (3 * D), r = i - j * 3 * D;
+                const int which = r / D, d = r - which * D;
+                const size_t tok = (size_t)(start + base + j);
+                const float* src = which == 0 ? q + tok * qk + (size_t)g * D + d
+                                 : which == 1 ? k + tok * qk + (size_t)g * D + d
+                                              : decay + tok * hd + (size_t)h * D + d;
+                gd_copy4(dst0 + (size_t)j * per_tok + which * D + d, src);
+            }
+        }
+        for (int i = threadIdx.x; i < here * (ncols + 1); i += GD_THREADS) {
+            const int j = i / (ncols + 1), c = i - j * (ncols + 1);
+            const size_t tok = (size_t)(start + base + j);
+            float* dst = dst0 + (size_t)j * per_tok + 3 * D;
+            if (c < ncols) gd_copy4(dst + c, v + tok * vv + (size_t)h * a.VD + col0 + c);
+            else gd_copy4(dst + COLS, beta + tok * a.H + h);
+        }
+    };
+
+    fetch(0, 0);
+    cp_async_commit();
     float* s_col = state + (size_t)a.slots[e] * a.state_stride + a.state_offset +
                    ((size_t)h * a.VD + (live ? col : 0)) * D;
-    float s[GD_ROWS];
+    float s[R];
 #pragma unroll
-    for (int i = 0; i < GD_ROWS; ++i) {
+    for (int i = 0; i < R; ++i) {
         const int r = lane + L * i;
         s[i] = (live && r < D) ? s_col[r] : 0.f;
     }
-    const int qk = a.G * D, hd = a.H * D, vv = a.H * a.VD;
-    for (int base = 0; base < n; base += a.chunk) {
+    int buf = 0;
+    for (int base = 0; base < n; base += a.chunk, buf ^= 1) {
+        if (base + a.chunk < n) fetch(buf ^ 1, base + a.chunk);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
         const int here = min(a.chunk, n - base);
-        __syncthreads();
-        for (int i = threadIdx.x; i < here * D; i += GD_THREADS) {
-            const int j = i / D, d = i - j * D;
-            const size_t tok = (size_t)(start + base + j);
-            float* dst = stage + (size_t)j * 3 * D;
-            dst[d] = q[tok * qk + (size_t)g * D + d];
-            dst[D + d] = k[tok * qk + (size_t)g * D + d];
-            dst[2 * D + d] = decay[tok * hd + (size_t)h * D + d];
-        }
-        __syncthreads();
-        for (int j = 0; j < here; ++j) {
-            const size_t tok = (size_t)(start + base + j);
-            const float* qs = stage + (size_t)j * 3 * D;
+        const float* tokp = stage + (size_t)buf * a.chunk * per_tok;
+        for (int j = 0; j < here; ++j, tokp += per_tok) {
+            const float* qs = tokp;
             const float* ks = qs + D;
             const float* gs = ks + D;
-            float r = 0.f, p = 0.f, qkdot = 0.f;
+            float r4[4] = {0.f, 0.f, 0.f, 0.f}, p4[4] = {0.f, 0.f, 0.f, 0.f}, qkdot = 0.f;
 #pragma unroll
-            for (int i = 0; i < GD_ROWS; ++i) {
+            for (int i = 0; i < R; ++i) {
                 const int row = lane + L * i;
                 if (row < D) {
+                    const float kr = ks[row], qr = qs[row];
                     s[i] *= gs[row];
-                    r = fmaf(ks[row], s[i], r);
-                    p = fmaf(qs[row], s[i], p);
-                    qkdot = fmaf(qs[row], ks[row], qkdot);
+                    r4[i & 3] = fmaf(kr, s[i], r4[i & 3]);
+                    p4[i & 3] = fmaf(qr, s[i], p4[i & 3]);
+                    qkdot = fmaf(qr, kr, qkdot);
                 }
             }
+            float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
+            float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) {
                 r += __shfl_xor_sync(0xffffffffu, r, o);
                 p += __shfl_xor_sync(0xffffffffu, p, o);
                 qkdot += __shfl_xor_sync(0xffffffffu, qkdot, o);
             }
-            const float vt = live ? v[tok * vv + (size_t)h * a.VD + col] : 0.f;
-            const float u = beta[tok * a.H + h] * (vt - r);
+            const float u = tokp[3 * D + COLS] * (tokp[3 * D + mycol] - r);
 #pragma unroll
-            for (int i = 0; i < GD_ROWS; ++i) {
+            for (int i = 0; i < R; ++i) {
                 const int row = lane + L * i;
                 if (row < D) s[i] = fmaf(ks[row], u, s[i]);
             }
-            if (live && lane == 0) a.out[tok * vv + (size_t)h * a.VD + col] = fmaf(qkdot, u, p);
+            if (live && lane == 0)
+                a.out[(size_t)(start + base + j) * vv + (size_t)h * a.VD + col] = fmaf(qkdot, u, p);
         }
+        __syncthreads();                       // the buffer is free for the chunk after next
     }
+    cp_async_wait<0>();
     if (live) {
 #pragma unroll
-        for (int i = 0; i < GD_ROWS; ++i) {
+        for (int i = 0; i < R; ++i) {
             const int r = lane + L * i;
             if (r < D) s_col[r] = s[i];
         }
@@ -234,28 +293,51 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
 MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, const float* beta,
                                const float* decay, const int* qo_indptr, const int* slots,
                                float* state, long long state_stride, long long state_offset,
-                               float* out, int entries, int H, int G, int D, int VD, void* stream) {
+                               float* out, int entries, int max_q_len, int H, int G, int D, int VD,
+                               void* stream) {
     if (entries <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || VD <= 0 || D > 32 * GD_ROWS) return -1;
-    if (entries > 2147483647 / 1 || H > 65535) return -1;
+    if (H > 65535) return -1;
+    // lanes a column: four rows a lane where that fills at most a warp
     int L = 4;
-    while (L * GD_ROWS < D) L *= 2;
-    // few columns a block where the value size is small, so that the lanes are not idle
-    int chunk = 16;
-    while (chunk > 1 && (size_t)chunk * 3 * D * sizeof(float) > 40 * 1024) chunk /= 2;
-    const size_t smem = (size_t)chunk * 3 * D * sizeof(float);
+    while (L < 32 && L * 4 < D) L *= 2;
+    const int R = D <= L * 4 ? 4 : (D <= L * 8 ? 8 : 16);
+    const int cols = GD_THREADS / L;
+    // tokens staged at a time: 16, fewer where a token's rows are wide or the entries short
+    int chunk = GD_CHUNK;
+    while (chunk > 1 && (chunk / 2 >= max_q_len ||
+                         (size_t)2 * chunk * (3 * D + cols + 4) * sizeof(float) > 64 * 1024))
+        chunk /= 2;
+    const size_t smem = (size_t)2 * chunk * (3 * D + cols + 4) * sizeof(float);
     DeltaScanArgs a{q, k, v, beta, decay, qo_indptr, slots, state, state_stride, state_offset, out,
                     H, G, D, VD, chunk};
     cudaStream_t s = (cudaStream_t)stream;
-    const int cols = GD_THREADS / L;
     dim3 grid(entries, H, (VD + cols - 1) / cols);
     if (grid.z > 65535) return -1;
-    switch (L) {
-        case 4: mstar_launch((delta_scan_kernel<4>), grid, dim3(GD_THREADS), smem, s, a); break;
-        case 8: mstar_launch((delta_scan_kernel<8>), grid, dim3(GD_THREADS), smem, s, a); break;
-        case 16: mstar_launch((delta_scan_kernel<16>), grid, dim3(GD_THREADS), smem, s, a); break;
-        default: mstar_launch((delta_scan_kernel<32>), grid, dim3(GD_THREADS), smem, s, a); break;
-    }
+    // 16-byte copies want whole pieces and aligned rows (the buffers are allocations of their own)
+    const bool vec = D % 4 == 0 && (state_offset % 4) == 0 &&
+                     ((uintptr_t)q % 16 == 0) && ((uintptr_t)k % 16 == 0) && ((uintptr_t)decay % 16 == 0);
+#define GO(LL, RR)                                                                                \
+    do {                                                                                          \
+        if (vec) {                                                                                \
+            if (smem > 48 * 1024)                                                                 \
+                cudaFuncSetAttribute(delta_scan_kernel<LL, RR, true>,                             \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+            mstar_launch((delta_scan_kernel<LL, RR, true>), grid, dim3(GD_THREADS), smem, s, a);  \
+        } else {                                                                                  \
+            if (smem > 48 * 1024)                                                                 \
+                cudaFuncSetAttribute(delta_scan_kernel<LL, RR, false>,                            \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+            mstar_launch((delta_scan_kernel<LL, RR, false>), grid, dim3(GD_THREADS), smem, s, a); \
+        }                                                                                         \
+    } while (0)
+    if (L == 4) GO(4, 4);
+    else if (L == 8) GO(8, 4);
+    else if (L == 16) GO(16, 4);
+    else if (R == 4) GO(32, 4);
+    else if (R == 8) GO(32, 8);
+    else GO(32, 16);
+#undef GO
     return launch_status();
 }
 

@@ -32,7 +32,8 @@ struct HyperArgs {
     float eps;
 };
 
-template <typename A, typename W>
+// SM: the compiled capacity for copies (1, 2, 4 or 8), the smallest that holds S.
+template <typename A, typename W, int SM>
 __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(HyperArgs a) {
     extern __shared__ float u_row[];          // [width]: what the norm reads (read mode)
     __shared__ float scratch[32];
@@ -59,42 +60,74 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(HyperArgs a) {
     __syncthreads();
     float* xt = x + (size_t)t * S * a.width;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < a.width; c += HC_THREADS) {
-        float old[HC_MAX_STREAMS], now[HC_MAX_STREAMS];
+    // four columns a thread at a time (16-byte accesses) where the width allows, else one
+    const int V = (a.width % 4 == 0) ? 4 : 1;
+    for (int c = threadIdx.x * V; c < a.width; c += HC_THREADS * V) {
+        float old[SM][4], y[4] = {0.f, 0.f, 0.f, 0.f}, u[4] = {0.f, 0.f, 0.f, 0.f};
+        if (V == 4) {
+            if (init != nullptr) {
+                const float4 r = *reinterpret_cast<const float4*>(init + (size_t)t * a.width + c);
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
-            if (s < S) old[s] = init != nullptr ? init[(size_t)t * a.width + c] : xt[(size_t)s * a.width + c];
-        if (y1 != nullptr) {
-            float y = a.a * to_float(y1[(size_t)t * a.width + c]);
-            if (y2 != nullptr) y = fmaf(a.b, to_float(y2[(size_t)t * a.width + c]), y);
-            if (y_bias != nullptr) y += to_float(y_bias[c]);
+                for (int s = 0; s < SM; ++s)
+                    if (s < S) { old[s][0] = r.x; old[s][1] = r.y; old[s][2] = r.z; old[s][3] = r.w; }
+            } else {
 #pragma unroll
-            for (int to = 0; to < HC_MAX_STREAMS; ++to)
-                if (to < S) {
-                    float v = 0.f;
-#pragma unroll
-                    for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                        if (s < S) v = fmaf(mix[s * S + to], old[s], v);
-                    now[to] = fmaf(outw[to], y, v);
-                }
-        } else {
-#pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
-                if (s < S) now[s] = old[s];
-        }
-        float u = 0.f;
-#pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
-            if (s < S) {
-                if (store) xt[(size_t)s * a.width + c] = now[s];
-                u = fmaf(inw[s], now[s], u);
+                for (int s = 0; s < SM; ++s)
+                    if (s < S) {
+                        const float4 r = *reinterpret_cast<const float4*>(xt + (size_t)s * a.width + c);
+                        old[s][0] = r.x; old[s][1] = r.y; old[s][2] = r.z; old[s][3] = r.w;
+                    }
             }
-        if (sum_mode) {
-            a.sum_out[(size_t)blockIdx.x * a.width + c] = u;
         } else {
-            u_row[c] = u;
-            ss = fmaf(u, u, ss);
+#pragma unroll
+            for (int s = 0; s < SM; ++s)
+                if (s < S) old[s][0] = init != nullptr ? init[(size_t)t * a.width + c] : xt[(size_t)s * a.width + c];
         }
+        if (y1 != nullptr) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (e < V) {
+                    y[e] = a.a * to_float(y1[(size_t)t * a.width + c + e]);
+                    if (y2 != nullptr) y[e] = fmaf(a.b, to_float(y2[(size_t)t * a.width + c + e]), y[e]);
+                    if (y_bias != nullptr) y[e] += to_float(y_bias[c + e]);
+                }
+        }
+#pragma unroll
+        for (int to = 0; to < SM; ++to)
+            if (to < S) {
+                float nv[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (e < V) {
+                        float v = old[to][e];
+                        if (y1 != nullptr) {
+                            v = 0.f;
+#pragma unroll
+                            for (int s = 0; s < SM; ++s)
+                                if (s < S) v = fmaf(mix[s * S + to], old[s][e], v);
+                            v = fmaf(outw[to], y[e], v);
+                        }
+                        nv[e] = v;
+                        u[e] = fmaf(inw[to], v, u[e]);
+                    }
+                if (store) {
+                    if (V == 4)
+                        *reinterpret_cast<float4*>(xt + (size_t)to * a.width + c) =
+                            make_float4(nv[0], nv[1], nv[2], nv[3]);
+                    else
+                        xt[(size_t)to * a.width + c] = nv[0];
+                }
+            }
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            if (e < V) {
+                if (sum_mode) {
+                    a.sum_out[(size_t)blockIdx.x * a.width + c + e] = u[e];
+                } else {
+                    u_row[c + e] = u[e];
+                    ss = fmaf(u[e], u[e], ss);
+                }
+            }
     }
     if (sum_mode || a.normed == nullptr) return;
     const float total = block_sum(ss, scratch);
@@ -123,21 +156,29 @@ MSTAR_API int mstar_hyper_step(float* x, const float* init, const void* y1, cons
     HyperArgs h{x, init, y1, y2, y_bias, a, b, mix, out, in, norm_weight, normed, rows, sum_out,
                 streams, width, eps};
     cudaStream_t s = (cudaStream_t)stream;
-#define GO(A, W)                                                                                  \
+#define GO1(A, W, SM)                                                                             \
     do {                                                                                          \
         static size_t configured = 0;                                                             \
         if (smem > 48 * 1024 && smem > configured) {                                              \
-            cudaFuncSetAttribute(hyper_step_kernel<A, W>,                                         \
+            cudaFuncSetAttribute(hyper_step_kernel<A, W, SM>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
             configured = smem;                                                                    \
         }                                                                                         \
-        mstar_launch((hyper_step_kernel<A, W>), dim3(blocks), dim3(HC_THREADS), smem, s, h);      \
+        mstar_launch((hyper_step_kernel<A, W, SM>), dim3(blocks), dim3(HC_THREADS), smem, s, h);  \
+    } while (0)
+#define GO(A, W)                                                                                  \
+    do {                                                                                          \
+        if (streams == 1) GO1(A, W, 1);                                                           \
+        else if (streams == 2) GO1(A, W, 2);                                                      \
+        else if (streams <= 4) GO1(A, W, 4);                                                      \
+        else GO1(A, W, 8);                                                                        \
     } while (0)
     if (act_dtype == MSTAR_F32) {
         if (weight_dtype == MSTAR_F32) GO(float, float); else GO(float, bf16);
     } else {
         if (weight_dtype == MSTAR_F32) GO(bf16, float); else GO(bf16, bf16);
     }
+#undef GO1
 #undef GO
     return launch_status();
 }

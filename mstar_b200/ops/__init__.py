@@ -1619,9 +1619,11 @@ def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_proj: torch.Tensor
 
 
 def delta_scan(q, k, v, beta, decay, qo_indptr, slots, state: torch.Tensor, entries: int,
-               heads: int, kv_heads: int, dim: int, vdim: int, taps: int) -> torch.Tensor:
+               heads: int, kv_heads: int, dim: int, vdim: int, taps: int,
+               max_q_len: int = 1 << 30) -> torch.Tensor:
     """The gated delta rule over the tokens of ``entries`` batch entries, each continuing the
-    matrix in its slot (updated in place).  Returns float [tokens, heads * vdim]."""
+    matrix in its slot (updated in place).  ``max_q_len``: the longest entry (a bound will do;
+    short entries stage fewer tokens at a time).  Returns float [tokens, heads * vdim]."""
     _need_cuda(q, k, v, beta, decay, qo_indptr, slots, state)
     for t in (q, k, v, beta, decay):
         assert t.dtype == torch.float32 and t.is_contiguous()
@@ -1632,7 +1634,8 @@ def delta_scan(q, k, v, beta, decay, qo_indptr, slots, state: torch.Tensor, entr
     code = lib.get("gated_delta").mstar_delta_scan(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(),
         qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0), offset,
-        out.data_ptr(), entries, heads, kv_heads, dim, vdim, _stream())
+        out.data_ptr(), entries, int(min(max_q_len, 1 << 30)), heads, kv_heads, dim, vdim,
+        _stream())
     if code == -1:
         raise KernelError(f"delta-rule scan refuses heads={heads}, kv_heads={kv_heads}, dim={dim} "
                           "(dim at most 512)")

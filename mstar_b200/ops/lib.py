@@ -47,7 +47,7 @@ _SIGNATURES = {
         "mstar_delta_prepare": [_vp, _i, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _vp,
                                 _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp],
         "mstar_delta_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i,
-                             _i, _vp],
+                             _i, _i, _vp],
         "mstar_delta_finish": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
     },
     "matrix_memory": {

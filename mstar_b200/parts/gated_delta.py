@@ -83,7 +83,7 @@ class GatedDelta:
         ops.conv_state_advance(proj, channels, s.conv, ctx.qo_indptr, ctx.slots, cache.state,
                                ctx.num_entries)
         o = ops.delta_scan(q, k, v, beta, decay, ctx.qo_indptr, ctx.slots, cache.state,
-                           ctx.num_entries, H, G, D, VD, s.conv)
+                           ctx.num_entries, H, G, D, VD, s.conv, max_q_len=ctx.max_q_len)
         y = ops.delta_finish(o, gate, self.norm_weight, H, VD, s.norm_eps, self.runtime.dtype,
                              self.out_scale)
         return ops.linear(y, self.w_out, static_weights=True)
