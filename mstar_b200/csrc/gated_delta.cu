@@ -10,7 +10,8 @@
 //            and key channel, a = the low-rank projection's output [H*D].
 //   scan     per head, token after token:  S = decay * S (rows);  u = beta (v - S^T k);
 //            S += k u^T;  o = S^T q.  Computed as  r = (decay*S)^T k,  p = (decay*S)^T q,
-//            u = beta (v - r),  o = p + (q . k) u,  so that one round of shuffles serves a token.
+//            u = beta (v - r),  o = p + (q . k) u:  the chain from token to token holds one
+//            round of shuffles (r); the read-out's round runs beside the next token.
 //   finish   o / rms(o per head) * weight * sigmoid(gate), handed on in the activation type.
 //
 // A slot is [(taps - 1) * (2 G D + H VD) convolution inputs | S^T as [H][VD][D]], float.
@@ -180,7 +181,8 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
     const int col = col0 + mycol;
     const bool live = col < a.VD;
     const int D = a.D;
-    const int per_tok = 3 * D + COLS + 4;              // q, k, decay, values, beta (+ padding)
+    constexpr int DP = L * R;                          // rows as the lanes see them, zeros past D
+    const int per_tok = 3 * DP + COLS + 4;             // q, k, decay, values, beta (+ padding)
     const unsigned long long waited = pdl_wait();
     const float* q = pdl_after(a.q, waited);
     const float* k = pdl_after(a.k, waited);
@@ -196,37 +198,38 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
     auto fetch = [&](int buf, int base) {
         const int here = min(a.chunk, n - base);
         float* dst0 = stage + (size_t)buf * a.chunk * per_tok;
-        if constexpr (VEC) {
-            const int pieces = D / 4;
-            for (int i = threadIdx.x; i < here * 3 * pieces; i += GD_THREADS) {
-                const int j = i / (3 * pieces), r = i - j * 3 * pieces;
-                const int which = r / pieces, d = (r - which * pieces) * 4;
-                const size_t tok = (size_t)(start + base + j);
-                const float* src = which == 0 ? q + tok * qk + (size_t)g * D + d
-                                 : which == 1 ? k + tok * qk + (size_t)g * D + d
-                                              : decay + tok * hd + (size_t)h * D + d;
-                gd_copy16(dst0 + (size_t)j * per_tok + which * D + d, src);
-            }
-        } else {
-            for (int i = threadIdx.x; i < here * 3 * D; i += GD_THREADS) {
-                const int j = i / (3 * D), r = i - j * 3 * D;
-                const int which = r / D, d = r - which * D;
-                const size_t tok = (size_t)(start + base + j);
-                const float* src = which == 0 ? q + tok * qk + (size_t)g * D + d
-                                 : which == 1 ? k + tok * qk + (size_t)g * D + d
-                                              : decay + tok * hd + (size_t)h * D + d;
-                gd_copy4(dst0 + (size_t)j * per_tok + which * D + d, src);
-            }
+        // copy i of the chunk is piece r of token j; both move on by fixed steps from copy to
+        // copy, so the loop divides nothing
+        const int unit = VEC ? 4 : 1;
+        const int per = 3 * (D / unit);                 // copies a token
+        const int dj = GD_THREADS / per, dr = GD_THREADS % per;
+        int j = threadIdx.x / per, r = threadIdx.x % per;
+        for (; j < here; j += dj, r += dr) {
+            if (r >= per) { r -= per; ++j; if (j >= here) break; }
+            const int which = r / (D / unit), d = (r - which * (D / unit)) * unit;
+            const size_t tok = (size_t)(start + base + j);
+            const float* src = which == 0 ? q + tok * qk + (size_t)g * D + d
+                             : which == 1 ? k + tok * qk + (size_t)g * D + d
+                                          : decay + tok * hd + (size_t)h * D + d;
+            float* dst = dst0 + (size_t)j * per_tok + which * DP + d;
+            if constexpr (VEC) gd_copy16(dst, src); else gd_copy4(dst, src);
         }
         for (int i = threadIdx.x; i < here * (ncols + 1); i += GD_THREADS) {
             const int j = i / (ncols + 1), c = i - j * (ncols + 1);
             const size_t tok = (size_t)(start + base + j);
-            float* dst = dst0 + (size_t)j * per_tok + 3 * D;
+            float* dst = dst0 + (size_t)j * per_tok + 3 * DP;
             if (c < ncols) gd_copy4(dst + c, v + tok * vv + (size_t)h * a.VD + col0 + c);
             else gd_copy4(dst + COLS, beta + tok * a.H + h);
         }
     };
 
+    // rows past D read as zeros (q, k) whatever the chunk: no copy ever writes there
+    if (DP > D) {
+        for (int i = threadIdx.x; i < 2 * a.chunk * 3 * (DP - D); i += GD_THREADS) {
+            const int j = i / (3 * (DP - D)), r = i - j * 3 * (DP - D);
+            stage[(size_t)j * per_tok + (r / (DP - D)) * DP + D + r % (DP - D)] = 0.f;
+        }
+    }
     fetch(0, 0);
     cp_async_commit();
     float* s_col = state + (size_t)a.slots[e] * a.state_stride + a.state_offset +
@@ -238,6 +241,8 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
         s[i] = (live && r < D) ? s_col[r] : 0.f;
     }
     int buf = 0;
+    float o_prev = 0.f;                        // the last token's read-out, not yet summed
+    int prev_tok = -1;
     for (int base = 0; base < n; base += a.chunk, buf ^= 1) {
         if (base + a.chunk < n) fetch(buf ^ 1, base + a.chunk);
         cp_async_commit();
@@ -245,42 +250,64 @@ __global__ void __launch_bounds__(GD_THREADS) delta_scan_kernel(DeltaScanArgs a)
         __syncthreads();
         const int here = min(a.chunk, n - base);
         const float* tokp = stage + (size_t)buf * a.chunk * per_tok;
-        for (int j = 0; j < here; ++j, tokp += per_tok) {
-            const float* qs = tokp;
-            const float* ks = qs + D;
-            const float* gs = ks + D;
+        // the rows of the token after this one are read from shared memory while this one's
+        // sums go round the lanes
+        float qn[R], kn[R], gn[R], vn, bn;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            qn[i] = tokp[lane + L * i];
+            kn[i] = tokp[DP + lane + L * i];
+            gn[i] = tokp[2 * DP + lane + L * i];
+        }
+        vn = tokp[3 * DP + mycol];
+        bn = tokp[3 * DP + COLS];
+        for (int j = 0; j < here; ++j) {
+            float qr[R], kr[R], gr[R];
+#pragma unroll
+            for (int i = 0; i < R; ++i) { qr[i] = qn[i]; kr[i] = kn[i]; gr[i] = gn[i]; }
+            const float vt = vn, bt = bn;
+            tokp += per_tok;
+            if (j + 1 < here) {
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    qn[i] = tokp[lane + L * i];
+                    kn[i] = tokp[DP + lane + L * i];
+                    gn[i] = tokp[2 * DP + lane + L * i];
+                }
+                vn = tokp[3 * DP + mycol];
+                bn = tokp[3 * DP + COLS];
+            }
             float r4[4] = {0.f, 0.f, 0.f, 0.f}, p4[4] = {0.f, 0.f, 0.f, 0.f}, qkdot = 0.f;
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                const int row = lane + L * i;
-                if (row < D) {
-                    const float kr = ks[row], qr = qs[row];
-                    s[i] *= gs[row];
-                    r4[i & 3] = fmaf(kr, s[i], r4[i & 3]);
-                    p4[i & 3] = fmaf(qr, s[i], p4[i & 3]);
-                    qkdot = fmaf(qr, kr, qkdot);
-                }
+                s[i] *= gr[i];
+                r4[i & 3] = fmaf(kr[i], s[i], r4[i & 3]);
+                p4[i & 3] = fmaf(qr[i], s[i], p4[i & 3]);
+                qkdot = fmaf(qr[i], kr[i], qkdot);
             }
+            // a warp issues in order, so a round of shuffles costs its latency wherever it
+            // stands: the read-out of the token before goes round together with this token's r
             float r = (r4[0] + r4[1]) + (r4[2] + r4[3]);
-            float p = (p4[0] + p4[1]) + (p4[2] + p4[3]);
+            float o_red = o_prev;
 #pragma unroll
             for (int o = L / 2; o > 0; o >>= 1) {
                 r += __shfl_xor_sync(0xffffffffu, r, o);
-                p += __shfl_xor_sync(0xffffffffu, p, o);
-                qkdot += __shfl_xor_sync(0xffffffffu, qkdot, o);
+                o_red += __shfl_xor_sync(0xffffffffu, o_red, o);
             }
-            const float u = tokp[3 * D + COLS] * (tokp[3 * D + mycol] - r);
+            if (prev_tok >= 0 && live && lane == 0)
+                a.out[(size_t)prev_tok * vv + (size_t)h * a.VD + col] = o_red;
+            const float u = bt * (vt - r);
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int row = lane + L * i;
-                if (row < D) s[i] = fmaf(ks[row], u, s[i]);
-            }
-            if (live && lane == 0)
-                a.out[(size_t)(start + base + j) * vv + (size_t)h * a.VD + col] = fmaf(qkdot, u, p);
+            for (int i = 0; i < R; ++i) s[i] = fmaf(kr[i], u, s[i]);
+            o_prev = fmaf(qkdot, u, (p4[0] + p4[1]) + (p4[2] + p4[3]));
+            prev_tok = start + base + j;
         }
         __syncthreads();                       // the buffer is free for the chunk after next
     }
     cp_async_wait<0>();
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) o_prev += __shfl_xor_sync(0xffffffffu, o_prev, o);
+    if (live && lane == 0) a.out[(size_t)prev_tok * vv + (size_t)h * a.VD + col] = o_prev;
     if (live) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
@@ -298,17 +325,25 @@ MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, c
     if (entries <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || VD <= 0 || D > 32 * GD_ROWS) return -1;
     if (H > 65535) return -1;
-    // lanes a column: four rows a lane where that fills at most a warp
+    // lanes a column: four rows a lane where that fills at most a warp (MSTAR_DELTA_LANES=8
+    // or 16: that many from 128 rows on, for measurements)
     int L = 4;
     while (L < 32 && L * 4 < D) L *= 2;
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("MSTAR_DELTA_LANES");
+        forced = e != nullptr ? atoi(e) : 0;
+    }
+    if (L == 32 && (forced == 8 || forced == 16) && D <= forced * 16) L = forced;
     const int R = D <= L * 4 ? 4 : (D <= L * 8 ? 8 : 16);
     const int cols = GD_THREADS / L;
+    // (the staged rows are padded to L * R)
     // tokens staged at a time: 16, fewer where a token's rows are wide or the entries short
     int chunk = GD_CHUNK;
     while (chunk > 1 && (chunk / 2 >= max_q_len ||
-                         (size_t)2 * chunk * (3 * D + cols + 4) * sizeof(float) > 64 * 1024))
+                         (size_t)2 * chunk * (3 * L * R + cols + 4) * sizeof(float) > 64 * 1024))
         chunk /= 2;
-    const size_t smem = (size_t)2 * chunk * (3 * D + cols + 4) * sizeof(float);
+    const size_t smem = (size_t)2 * chunk * (3 * L * R + cols + 4) * sizeof(float);
     DeltaScanArgs a{q, k, v, beta, decay, qo_indptr, slots, state, state_stride, state_offset, out,
                     H, G, D, VD, chunk};
     cudaStream_t s = (cudaStream_t)stream;
@@ -332,8 +367,12 @@ MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, c
         }                                                                                         \
     } while (0)
     if (L == 4) GO(4, 4);
-    else if (L == 8) GO(8, 4);
-    else if (L == 16) GO(16, 4);
+    else if (L == 8 && R == 4) GO(8, 4);
+    else if (L == 8 && R == 8) GO(8, 8);
+    else if (L == 8) GO(8, 16);
+    else if (L == 16 && R == 4) GO(16, 4);
+    else if (L == 16 && R == 8) GO(16, 8);
+    else if (L == 16) GO(16, 16);
     else if (R == 4) GO(32, 4);
     else if (R == 8) GO(32, 8);
     else GO(32, 16);
