@@ -45,9 +45,28 @@ __device__ __forceinline__ float gd_softplus(float z) {
     return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
 }
 
+// The convolved and activated value of channel c of token t (the `local`-th of its portion).
+template <typename W>
+__device__ __forceinline__ float delta_conv_silu(const float* row, const float* slot, const W* cw,
+                                                 int c, int channels, int local,
+                                                 const DeltaPrepArgs& a) {
+    const int keep = a.taps - 1;
+    float y = 0.f;
+    for (int j = 0; j < a.taps; ++j) {
+        const int back = keep - j;                       // rows before this token
+        const float u = back <= local ? *(row - (ptrdiff_t)back * a.row_stride + c)
+                                      : slot[(size_t)(keep + local - back) * channels + c];
+        y = fmaf(to_float(cw[(size_t)c * a.taps + j]), u, y);
+    }
+    return y / (1.f + expf(-y));
+}
+
+// A block per token, or, with few tokens, several: a token's work comes in units that a warp
+// takes whole (a q head or a k head with its unit norm, the values of a head, the decays of a
+// head with its write strength), dealt out among the warps of gridDim.y blocks.
 template <typename W>
 __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
-    extern __shared__ float ch[];             // [2 G D + H VD] convolved, activated channels
+    extern __shared__ float ch[];             // [warps][D] a q or k head after its convolution
     const int t = blockIdx.x;
     const int qk = a.G * a.D, vv = a.H * a.VD, channels = 2 * qk + vv;
     const W* cw = reinterpret_cast<const W*>(a.conv_w);
@@ -57,40 +76,42 @@ __global__ void __launch_bounds__(256) delta_prepare_kernel(DeltaPrepArgs a) {
     const float* state = pdl_after(a.state, waited);
     const int e = a.token_req[t];
     const int local = t - a.qo_indptr[e];
-    const float* slot = state + (size_t)a.slots[e] * a.state_stride;
+    const float* slot = a.taps > 1 ? state + (size_t)a.slots[e] * a.state_stride : nullptr;
     const float* row = proj + (size_t)t * a.row_stride;
-    const int keep = a.taps - 1;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-        float y = 0.f;
-        for (int j = 0; j < a.taps; ++j) {
-            const int back = keep - j;                   // rows before this token
-            const float u = back <= local ? *(row - (ptrdiff_t)back * a.row_stride + c)
-                                          : slot[(size_t)(keep + local - back) * channels + c];
-            y = fmaf(to_float(cw[(size_t)c * a.taps + j]), u, y);
-        }
-        y = y / (1.f + expf(-y));
-        if (c >= 2 * qk) a.v[(size_t)t * vv + (c - 2 * qk)] = y;
-        else ch[c] = y;
-    }
-    __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    float* mine = ch + (size_t)warp * a.D;
     const float q_scale = rsqrtf((float)a.D);
-    for (int h = warp; h < 2 * a.G; h += nwarps) {        // q heads, then k heads
-        const float* src = ch + (size_t)h * a.D;
-        float ss = 0.f;
-        for (int d = lane; d < a.D; d += 32) ss = fmaf(src[d], src[d], ss);
-        ss = warp_sum(ss);
-        const bool is_q = h < a.G;
-        const float inv = rsqrtf(ss + a.unit_eps) * (is_q ? q_scale : 1.f);
-        float* dst = (is_q ? a.q : a.k) + (size_t)t * qk + (size_t)(is_q ? h : h - a.G) * a.D;
-        for (int d = lane; d < a.D; d += 32) dst[d] = src[d] * inv;
-    }
-    for (int h = threadIdx.x; h < a.H; h += blockDim.x)
-        a.beta[(size_t)t * a.H + h] = 1.f / (1.f + expf(-row[channels + h]));
-    const int hd = a.H * a.D;
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-        const float step = gd_softplus(a_proj[(size_t)t * hd + i] + a.dt_bias[i]);
-        a.decay[(size_t)t * hd + i] = expf(-a.a_exp[i / a.D] * step);
+    const int units = 2 * a.G + 2 * a.H;
+    for (int u = blockIdx.y * nwarps + warp; u < units; u += nwarps * gridDim.y) {
+        if (u < 2 * a.G) {                                // a q head, then the k heads
+            float ss = 0.f;
+            for (int d = lane; d < a.D; d += 32) {
+                const float y = delta_conv_silu(row, slot, cw, u * a.D + d, channels, local, a);
+                mine[d] = y;
+                ss = fmaf(y, y, ss);
+            }
+            ss = warp_sum(ss);
+            const bool is_q = u < a.G;
+            const float inv = rsqrtf(ss + a.unit_eps) * (is_q ? q_scale : 1.f);
+            float* dst = (is_q ? a.q : a.k) + (size_t)t * qk + (size_t)(is_q ? u : u - a.G) * a.D;
+            __syncwarp();
+            for (int d = lane; d < a.D; d += 32) dst[d] = mine[d] * inv;
+            __syncwarp();
+        } else if (u < 2 * a.G + a.H) {                   // the values of a head
+            const int h = u - 2 * a.G;
+            for (int d = lane; d < a.VD; d += 32)
+                a.v[(size_t)t * vv + (size_t)h * a.VD + d] =
+                    delta_conv_silu(row, slot, cw, 2 * qk + h * a.VD + d, channels, local, a);
+        } else {                                          // the decays of a head, its write strength
+            const int h = u - 2 * a.G - a.H;
+            const float rate = a.a_exp[h];
+            for (int d = lane; d < a.D; d += 32) {
+                const size_t i = (size_t)h * a.D + d;
+                const float step = gd_softplus(a_proj[(size_t)t * a.H * a.D + i] + a.dt_bias[i]);
+                a.decay[(size_t)t * a.H * a.D + i] = expf(-rate * step);
+            }
+            if (lane == 0) a.beta[(size_t)t * a.H + h] = 1.f / (1.f + expf(-row[channels + h]));
+        }
     }
 }
 
@@ -106,11 +127,22 @@ MSTAR_API int mstar_delta_prepare(const float* proj, int row_stride, const void*
     const int channels = 2 * G * D + H * VD;
     if (row_stride < channels + H) return -1;
     if (taps > 1 && (!slots || !state)) return -1;
-    const size_t smem = sizeof(float) * (size_t)(2 * G * D);
+    const int threads = 256, warps = threads / 32;
+    const size_t smem = sizeof(float) * (size_t)warps * D;
     if (smem > 160 * 1024) return -1;
     DeltaPrepArgs a{proj, row_stride, conv_w, a_proj, dt_bias, a_exp, token_req, qo_indptr, slots,
                     state, state_stride, q, k, v, beta, decay, H, G, D, VD, taps, unit_eps};
     cudaStream_t s = (cudaStream_t)stream;
+    // with fewer blocks than SMs a token's units go to several blocks
+    const int units = 2 * G + 2 * H;
+    int parts = 1;
+    if (tokens < device_sm_count()) {
+        parts = (units + warps - 1) / warps;
+        const int room = (2 * device_sm_count() + tokens - 1) / tokens;
+        if (parts > room) parts = room;
+        if (parts < 1) parts = 1;
+    }
+    dim3 grid(tokens, parts);
     static size_t configured_f = 0, configured_b = 0;
     if (weight_dtype == MSTAR_F32) {
         if (smem > 48 * 1024 && smem > configured_f) {
@@ -118,14 +150,14 @@ MSTAR_API int mstar_delta_prepare(const float* proj, int row_stride, const void*
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             configured_f = smem;
         }
-        mstar_launch((delta_prepare_kernel<float>), dim3(tokens), dim3(256), smem, s, a);
+        mstar_launch((delta_prepare_kernel<float>), grid, dim3(threads), smem, s, a);
     } else {
         if (smem > 48 * 1024 && smem > configured_b) {
             cudaFuncSetAttribute(delta_prepare_kernel<bf16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             configured_b = smem;
         }
-        mstar_launch((delta_prepare_kernel<bf16>), dim3(tokens), dim3(256), smem, s, a);
+        mstar_launch((delta_prepare_kernel<bf16>), grid, dim3(threads), smem, s, a);
     }
     return launch_status();
 }
