@@ -384,19 +384,19 @@ MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, c
     // 16-byte copies want whole pieces and aligned rows (the buffers are allocations of their own)
     const bool vec = D % 4 == 0 && (state_offset % 4) == 0 &&
                      ((uintptr_t)q % 16 == 0) && ((uintptr_t)k % 16 == 0) && ((uintptr_t)decay % 16 == 0);
+#define GO1(LL, RR, VV)                                                                           \
+    do {                                                                                          \
+        static size_t configured = 0;                                                             \
+        if (smem > 48 * 1024 && smem > configured) {                                              \
+            cudaFuncSetAttribute(delta_scan_kernel<LL, RR, VV>,                                   \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+            configured = smem;                                                                    \
+        }                                                                                         \
+        mstar_launch((delta_scan_kernel<LL, RR, VV>), grid, dim3(GD_THREADS), smem, s, a);        \
+    } while (0)
 #define GO(LL, RR)                                                                                \
     do {                                                                                          \
-        if (vec) {                                                                                \
-            if (smem > 48 * 1024)                                                                 \
-                cudaFuncSetAttribute(delta_scan_kernel<LL, RR, true>,                             \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-            mstar_launch((delta_scan_kernel<LL, RR, true>), grid, dim3(GD_THREADS), smem, s, a);  \
-        } else {                                                                                  \
-            if (smem > 48 * 1024)                                                                 \
-                cudaFuncSetAttribute(delta_scan_kernel<LL, RR, false>,                            \
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-            mstar_launch((delta_scan_kernel<LL, RR, false>), grid, dim3(GD_THREADS), smem, s, a); \
-        }                                                                                         \
+        if (vec) GO1(LL, RR, true); else GO1(LL, RR, false);                                      \
     } while (0)
     if (L == 4) GO(4, 4);
     else if (L == 8 && R == 4) GO(8, 4);
@@ -409,6 +409,7 @@ MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, c
     else if (R == 8) GO(32, 8);
     else GO(32, 16);
 #undef GO
+#undef GO1
     return launch_status();
 }
 
