@@ -159,10 +159,8 @@ class ResidualCopies:
         from .. import ops
 
         write = self.pending or {}
-        if not write:
-            streams = self.x.shape[1]
-            write = {"mix": _identity(streams, self.x.device),
-                     "out": torch.zeros(streams, dtype=torch.float32, device=self.x.device)}
+        if not write:                # nothing to write yet: the kernel still wants its tables
+            write = dict(zip(("mix", "out"), _no_write_tables(self.x.shape[1], self.x.device)))
         out = ops.hyper_step(self.x, init=self.init, **write, **read)
         if "rows" not in read:      # a sum leaves the copies as they were
             self.init = None
@@ -173,14 +171,16 @@ class ResidualCopies:
         return self.step(rows=rows)
 
 
-_IDENTITIES: dict = {}
+_NO_WRITE: dict = {}
 
 
-def _identity(n: int, device) -> torch.Tensor:
+def _no_write_tables(n: int, device) -> tuple:
+    """(identity mix, zero out) for a step that writes nothing; made once per size and device."""
     key = (n, str(device))
-    if key not in _IDENTITIES:
-        _IDENTITIES[key] = torch.eye(n, dtype=torch.float32, device=device).contiguous()
-    return _IDENTITIES[key]
+    if key not in _NO_WRITE:
+        _NO_WRITE[key] = (torch.eye(n, dtype=torch.float32, device=device).contiguous(),
+                          torch.zeros(n, dtype=torch.float32, device=device))
+    return _NO_WRITE[key]
 
 
 class HyperBlock:
