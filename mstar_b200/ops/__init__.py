@@ -1311,18 +1311,27 @@ def conv_state_advance(qkv: torch.Tensor, channels: int, taps: int, qo_indptr, s
 
 
 def sink_attention_splits(entries: int, max_q_len: int, num_heads: int, num_kv_heads: int,
-                          max_keys: int, sms: int | None = None) -> int:
+                          max_keys: int, sms: int | None = None, wide: int = 128) -> int:
     """Among how many CTAs the keys of a row tile are shared in the tensor-core kernel: one
-    where the row tiles alone fill the GPU, else enough for some two CTAs per SM, a split
-    keeping at least two tiles of 64 keys (one tile a CTA was measured and is slower: 27
-    against 24 us at 8 requests with 1,028 visible keys)."""
+    where the row tiles alone fill the GPU, else as many as still give every CTA an SM of its
+    own (a CTA's key and value stages take most of an SM's shared memory, so a CTA beyond one
+    per SM waits for a second wave: at 8 requests with 2,048 keys 8 splits take 23 us, 16
+    take 29, at 32 requests 2 take 62 and 5 take 76), a split keeping at least two tiles of
+    64 keys (one tile a CTA was measured and is slower: 27 against 24 us at 8 requests with
+    1,028 visible keys).  ``wide``: the larger of the key and value sizes; where the stages of
+    two CTAs fit an SM (sizes up to 64), two CTAs an SM are the target."""
     if sms is None:
         sms = num_sms()
     group = num_heads // num_kv_heads
-    ctas = max(1, -(-max_q_len * group // 64) * num_kv_heads * entries)
-    if ctas >= sms:
+    rows = max_q_len * group
+    ctas = max(1, -(-rows // 64) * num_kv_heads * entries)
+    padded = next((d for d in (32, 64, 96, 128, 256) if wide <= d), 256)
+    stages = 4 if (rows <= 64 and padded <= 128) else 2
+    smem = (2 * stages + 1) * 64 * (padded + 8) * 2
+    room = sms * min(2, max(1, (227 * 1024) // smem))
+    if ctas >= room:
         return 1
-    return max(1, min(-(-2 * sms // ctas), -(-max_keys // 64) // 2, 64))
+    return max(1, min(room // ctas, -(-max_keys // 64) // 2, 64))
 
 
 def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_req, cache_pos,
@@ -1359,7 +1368,7 @@ def sink_attention(q: torch.Tensor, kv_cache: torch.Tensor, block_table, token_r
         if window:
             max_keys = min(max_keys, window + keep_first + ctx.max_q_len)
         splits = sink_attention_splits(ctx.num_entries, ctx.max_q_len, num_heads, num_kv_heads,
-                                       max_keys, num_sms(q.device))
+                                       max_keys, num_sms(q.device), wide=max(head_dim, v_dim))
         scratch = None
         if splits > 1:
             scratch = torch.empty(tokens * num_heads * splits * (v_dim + 2), dtype=torch.float32,
