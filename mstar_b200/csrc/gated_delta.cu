@@ -413,6 +413,353 @@ MSTAR_API int mstar_delta_scan(const float* q, const float* k, const float* v, c
     return launch_status();
 }
 
+// ------------------------------------------------------------------ scan in pieces of 16 tokens
+// Within a piece of C tokens that starts from the state S0, with P_t the product of the decays
+// from the piece's first token up to t (per key channel):
+//   r_t = (P_t k_t) . S0 + sum_{j<t} A_tj u_j,        A_tj = sum_d k_t[d] k_j[d] prod_{i=j+1..t} g_i[d]
+//   u_t = beta_t (v_t - r_t)
+//   o_t = (P_t q_t) . S0 + sum_{j<=t} B_tj u_j,       B_tj = sum_d q_t[d] k_j[d] prod_{i=j+1..t} g_i[d]
+//   S_C = P_C S0 + sum_j (k_j prod_{i>j} g_i) u_j
+// A, B and the decayed rows do not depend on the state or on the value column: a first kernel
+// makes them for all pieces side by side (products of decays only, never a quotient).  The scan
+// then walks a piece with one dot product per token against S0 (a lane a token), a chain of C
+// scalar steps for u, and one pass over the rows for the new state.  All float.
+#define GC_TOKENS 16
+#define GC_MAX_ROWS 8        // rows of a column a lane keeps: D <= 256
+
+struct DeltaPieceArgs {
+    const float* q;
+    const float* k;
+    const float* decay;
+    const int* qo_indptr;
+    float* kt;                  // [H][tokens][D]  k_t P_t  (a piece's rows of a head lie together)
+    float* qt;                  // [H][tokens][D]  q_t P_t
+    float* kh;                  // [H][tokens][D]  k_t prod_{i>t} g_i
+    float* pc;                  // [entries][pieces][H][D]  P at the piece's last token
+    float* A;                   // [H][tokens][C]
+    float* B;                   // [H][tokens][C]
+    int H, G, D, max_pieces, tokens;
+};
+
+__global__ void __launch_bounds__(128) delta_pieces_kernel(DeltaPieceArgs a) {
+    extern __shared__ __align__(16) float sm[];          // k, q, g of the piece: [3][C][D]
+    const int piece = blockIdx.x, e = blockIdx.y, h = blockIdx.z;
+    const int D = a.D, g_head = h / (a.H / a.G);
+    const unsigned long long waited = pdl_wait();
+    const float* q = pdl_after(a.q, waited);
+    const float* k = pdl_after(a.k, waited);
+    const float* decay = pdl_after(a.decay, waited);
+    const int start = a.qo_indptr[e], n = a.qo_indptr[e + 1] - start;
+    const int base = piece * GC_TOKENS;
+    if (base >= n) return;
+    const int here = min(GC_TOKENS, n - base);
+    float* ks = sm;
+    float* qs = ks + GC_TOKENS * D;
+    float* gs = qs + GC_TOKENS * D;
+    const int qk = a.G * D, hd = a.H * D;
+    for (int i = threadIdx.x; i < here * D; i += blockDim.x) {
+        const int t = i / D, d = i - t * D;
+        const size_t tok = (size_t)(start + base + t);
+        ks[i] = k[tok * qk + (size_t)g_head * D + d];
+        qs[i] = q[tok * qk + (size_t)g_head * D + d];
+        gs[i] = decay[tok * hd + (size_t)h * D + d];
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float P = 1.f;
+        for (int t = 0; t < here; ++t) {
+            P *= gs[t * D + d];
+            const size_t o = ((size_t)h * a.tokens + start + base + t) * D + d;
+            a.kt[o] = ks[t * D + d] * P;
+            a.qt[o] = qs[t * D + d] * P;
+        }
+        a.pc[(((size_t)e * a.max_pieces + piece) * a.H + h) * D + d] = P;
+        float S = 1.f;
+        for (int t = here - 1; t >= 0; --t) {
+            a.kh[((size_t)h * a.tokens + start + base + t) * D + d] = ks[t * D + d] * S;
+            S *= gs[t * D + d];
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int j = warp; j < here; j += nwarps) {
+        float w[GC_MAX_ROWS];
+        float b = 0.f;
+#pragma unroll
+        for (int i = 0; i < GC_MAX_ROWS; ++i) {
+            const int d = lane + 32 * i;
+            w[i] = d < D ? ks[j * D + d] : 0.f;
+            if (d < D) b = fmaf(qs[j * D + d], w[i], b);
+        }
+        b = warp_sum(b);
+        if (lane == 0) a.B[((size_t)h * a.tokens + start + base + j) * GC_TOKENS + j] = b;
+        for (int t = j + 1; t < here; ++t) {
+            float av = 0.f, bv = 0.f;
+#pragma unroll
+            for (int i = 0; i < GC_MAX_ROWS; ++i) {
+                const int d = lane + 32 * i;
+                if (d < D) {
+                    w[i] *= gs[t * D + d];
+                    av = fmaf(ks[t * D + d], w[i], av);
+                    bv = fmaf(qs[t * D + d], w[i], bv);
+                }
+            }
+            av = warp_sum(av);
+            bv = warp_sum(bv);
+            if (lane == 0) {
+                const size_t o = ((size_t)h * a.tokens + start + base + t) * GC_TOKENS + j;
+                a.A[o] = av;
+                a.B[o] = bv;
+            }
+        }
+    }
+}
+
+struct DeltaChunkArgs {
+    const float* kt;
+    const float* qt;
+    const float* kh;
+    const float* pc;
+    const float* A;
+    const float* B;
+    const float* v;
+    const float* beta;
+    const int* qo_indptr;
+    const int* slots;
+    float* state;
+    long long state_stride;
+    long long state_offset;
+    float* out;
+    int H, VD, max_pieces, tokens;
+};
+
+#define GC_THREADS 256
+#define GC_COLS (GC_THREADS / 32)
+
+// R consecutive floats as one access.
+template <int R> struct GcVec;
+template <> struct GcVec<1> { typedef float T; };
+template <> struct GcVec<2> { typedef float2 T; };
+template <> struct GcVec<4> { typedef float4 T; };
+template <int R> __device__ __forceinline__ void gc_load(const float* p, float (&v)[R]) {
+    if constexpr (R == 8) {
+        const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else if constexpr (R == 4) {
+        const float4 a = *reinterpret_cast<const float4*>(p);
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+    } else if constexpr (R == 2) {
+        const float2 a = *reinterpret_cast<const float2*>(p);
+        v[0] = a.x; v[1] = a.y;
+    } else {
+        v[0] = p[0];
+    }
+}
+template <int R> __device__ __forceinline__ void gc_store(float* p, const float (&v)[R]) {
+    if constexpr (R == 8) {
+        reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+        reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else if constexpr (R == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    } else if constexpr (R == 2) {
+        *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    } else {
+        p[0] = v[0];
+    }
+}
+
+// A warp owns a value column of one head of one entry; its D = 32 R rows lie on the 32 lanes,
+// R consecutive rows a lane.  Per piece: the column goes to shared memory so that lane
+// (t, half) can take token t's two dot products over one half of the rows, four rows an
+// access (each lane starts its walk at another place, so that the lanes read different
+// banks); the scalar chain u_0 .. u_15 goes round by shuffles with every lane's row of A and B
+// in registers; then the new column, R rows an access.
+template <int R>
+__global__ void __launch_bounds__(GC_THREADS) delta_scan_pieces_kernel(DeltaChunkArgs a) {
+    extern __shared__ __align__(16) float sm[];
+    constexpr int C = GC_TOKENS, D = 32 * R, CP = C + 1;
+    constexpr int per_buf = 3 * C * D + 2 * C * CP + C * GC_COLS + C + D;
+    static_assert(per_buf % 4 == 0, "the second buffer starts on a 16-byte boundary");
+    float* col_sm = sm + 2 * per_buf;                    // [GC_COLS][D] the columns at a piece's start
+    const int e = blockIdx.x, h = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col0 = blockIdx.z * GC_COLS, col = col0 + warp;
+    const bool live = col < a.VD;
+    const int ncols = min(GC_COLS, a.VD - col0);
+    const unsigned long long waited = pdl_wait();
+    const float* kt = pdl_after(a.kt, waited);
+    const float* qt = pdl_after(a.qt, waited);
+    const float* kh = pdl_after(a.kh, waited);
+    const float* pc = pdl_after(a.pc, waited);
+    const float* A = pdl_after(a.A, waited);
+    const float* B = pdl_after(a.B, waited);
+    const float* v = pdl_after(a.v, waited);
+    const float* beta = pdl_after(a.beta, waited);
+    float* state = pdl_after(a.state, waited);
+    const int start = a.qo_indptr[e], n = a.qo_indptr[e + 1] - start;
+    if (n <= 0) return;
+    const int vv = a.H * a.VD;
+
+    auto fetch = [&](int buf, int piece) {
+        const int base = piece * C;
+        const int here = min(C, n - base);
+        float* dst = sm + buf * per_buf;
+        const size_t first = (size_t)h * a.tokens + start + base;      // the piece's first row
+        // the decayed rows of the piece's tokens lie together: one run of here * D floats each
+        for (int i = threadIdx.x * 4; i < here * D; i += GC_THREADS * 4) {
+            gd_copy16(dst + i, kt + first * D + i);
+            gd_copy16(dst + C * D + i, qt + first * D + i);
+            gd_copy16(dst + 2 * C * D + i, kh + first * D + i);
+        }
+        for (int i = threadIdx.x; i < here * C; i += GC_THREADS) {
+            const int t = i >> 4, j = i & 15;
+            gd_copy4(dst + 3 * C * D + t * CP + j, A + first * C + i);
+            gd_copy4(dst + 3 * C * D + C * CP + t * CP + j, B + first * C + i);
+        }
+        float* to = dst + 3 * C * D + 2 * C * CP;
+        for (int i = threadIdx.x; i < here * (ncols + 1); i += GC_THREADS) {
+            const int t = i / (ncols + 1), c = i - t * (ncols + 1);
+            const size_t tok = (size_t)(start + base + t);
+            if (c < ncols) gd_copy4(to + t * GC_COLS + c, v + tok * vv + (size_t)h * a.VD + col0 + c);
+            else gd_copy4(to + C * GC_COLS + t, beta + tok * a.H + h);
+        }
+        const float* pcs = pc + (((size_t)e * a.max_pieces + piece) * a.H + h) * D;
+        for (int d = threadIdx.x * 4; d < D; d += GC_THREADS * 4)
+            gd_copy16(to + C * GC_COLS + C + d, pcs + d);
+    };
+
+    const int pieces = (n + C - 1) / C;
+    fetch(0, 0);
+    cp_async_commit();
+    float* s_col = state + (size_t)a.slots[e] * a.state_stride + a.state_offset +
+                   ((size_t)h * a.VD + (live ? col : 0)) * D;
+    float s[R];
+    gc_load<R>(s_col + lane * R, s);
+    float* mycol = col_sm + warp * D;
+    const int t = lane & 15, half = lane >> 4;
+    constexpr int UNITS = D / 8;                         // 16-byte pieces of half a column
+    for (int piece = 0; piece < pieces; ++piece) {
+        const int buf = piece & 1;
+        if (piece + 1 < pieces) fetch(buf ^ 1, piece + 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const int here = min(C, n - piece * C);
+        const float* bufp = sm + buf * per_buf;
+        const float* kts = bufp;
+        const float* qts = kts + C * D;
+        const float* khs = qts + C * D;
+        const float* As = khs + C * D;
+        const float* Bs = As + C * CP;
+        const float* vs = Bs + C * CP;
+        const float* betas = vs + C * GC_COLS;
+        const float* pcs = betas + C;
+        gc_store<R>(mycol + lane * R, s);                // the column as every lane needs it
+        __syncwarp();
+        float arow[C], brow[C];
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            arow[j] = As[t * CP + j];
+            brow[j] = Bs[t * CP + j];
+        }
+        float r0 = 0.f, p0 = 0.f, r1 = 0.f, p1 = 0.f;
+        {
+            const float4* kr = reinterpret_cast<const float4*>(kts + t * D) + half * UNITS;
+            const float4* qr = reinterpret_cast<const float4*>(qts + t * D) + half * UNITS;
+            const float4* sr = reinterpret_cast<const float4*>(mycol) + half * UNITS;
+#pragma unroll
+            for (int i = 0; i < UNITS; ++i) {
+                const int unit = (lane + i) & (UNITS - 1);
+                const float4 k4 = kr[unit], q4 = qr[unit], s4 = sr[unit];
+                r0 = fmaf(k4.x, s4.x, r0); r1 = fmaf(k4.y, s4.y, r1);
+                r0 = fmaf(k4.z, s4.z, r0); r1 = fmaf(k4.w, s4.w, r1);
+                p0 = fmaf(q4.x, s4.x, p0); p1 = fmaf(q4.y, s4.y, p1);
+                p0 = fmaf(q4.z, s4.z, p0); p1 = fmaf(q4.w, s4.w, p1);
+            }
+        }
+        r0 += r1;
+        p0 += p1;
+        r0 += __shfl_xor_sync(0xffffffffu, r0, 16);
+        p0 += __shfl_xor_sync(0xffffffffu, p0, 16);
+        float c = vs[t * GC_COLS + warp] - r0;           // v_t - r_t as far as it is known
+        float o = p0;
+        float u[C];
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+            // lane j's c is complete here: every earlier u has been taken off it
+            const float uj = betas[j] * __shfl_sync(0xffffffffu, c, j);
+            u[j] = j < here ? uj : 0.f;
+            if (t > j) c = fmaf(-arow[j], u[j], c);
+            if (t >= j) o = fmaf(brow[j], u[j], o);
+        }
+        if (live && half == 0 && t < here)
+            a.out[(size_t)(start + piece * C + t) * vv + (size_t)h * a.VD + col] = o;
+        float pcv[R];
+        gc_load<R>(pcs + lane * R, pcv);
+#pragma unroll
+        for (int i = 0; i < R; ++i) s[i] *= pcv[i];
+#pragma unroll
+        for (int j = 0; j < C; ++j)
+            if (j < here) {                              // (rows past the piece are not staged)
+                float kv[R];
+                gc_load<R>(khs + j * D + lane * R, kv);
+#pragma unroll
+                for (int i = 0; i < R; ++i) s[i] = fmaf(kv[i], u[j], s[i]);
+            }
+        __syncthreads();                       // the buffer is free for the piece after next
+    }
+    cp_async_wait<0>();
+    if (live) gc_store<R>(s_col + lane * R, s);
+}
+
+// The scan in pieces, for key sizes of 32, 64, 128 or 256 (whole accesses a lane): `work` holds
+// 3 * tokens * H * D + entries * max_pieces * H * D + 2 * tokens * H * 16 floats.  Returns 0, a CUDA
+// error code, or -1 when the shape is refused.
+MSTAR_API int mstar_delta_scan_pieces(const float* q, const float* k, const float* v,
+                                      const float* beta, const float* decay, const int* qo_indptr,
+                                      const int* slots, float* state, long long state_stride,
+                                      long long state_offset, float* out, float* work, int tokens,
+                                      int entries, int max_q_len, int H, int G, int D, int VD,
+                                      void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || VD <= 0) return -1;
+    if (D != 32 && D != 64 && D != 128 && D != 256) return -1;
+    if (H > 65535 || entries > 65535 || (state_offset % 4) != 0 || (state_stride % 4) != 0) return -1;
+    const int max_pieces = (max_q_len + GC_TOKENS - 1) / GC_TOKENS;
+    const size_t thd = (size_t)tokens * H * D;
+    DeltaPieceArgs p{q, k, decay, qo_indptr, work, work + thd, work + 2 * thd, work + 3 * thd,
+                     nullptr, nullptr, H, G, D, max_pieces, tokens};
+    p.A = p.pc + (size_t)entries * max_pieces * H * D;
+    p.B = p.A + (size_t)tokens * H * GC_TOKENS;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem1 = (size_t)3 * GC_TOKENS * D * sizeof(float);
+    mstar_launch(delta_pieces_kernel, dim3(max_pieces, entries, H), dim3(128), smem1, s, p);
+    int code = launch_status();
+    if (code != 0) return code;
+    DeltaChunkArgs c{p.kt, p.qt, p.kh, p.pc, p.A, p.B, v, beta, qo_indptr, slots, state,
+                     state_stride, state_offset, out, H, VD, max_pieces, tokens};
+    const int per_buf = 3 * GC_TOKENS * D + 2 * GC_TOKENS * (GC_TOKENS + 1) + GC_TOKENS * GC_COLS +
+                        GC_TOKENS + D;
+    const size_t smem2 = ((size_t)2 * per_buf + (size_t)GC_COLS * D) * sizeof(float);
+    dim3 grid(entries, H, (VD + GC_COLS - 1) / GC_COLS);
+    if (grid.z > 65535) return -1;
+#define GO(RR)                                                                                    \
+    do {                                                                                          \
+        static size_t configured = 0;                                                             \
+        if (smem2 > 48 * 1024 && smem2 > configured) {                                            \
+            cudaFuncSetAttribute(delta_scan_pieces_kernel<RR>,                                    \
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2);        \
+            configured = smem2;                                                                   \
+        }                                                                                         \
+        mstar_launch((delta_scan_pieces_kernel<RR>), grid, dim3(GC_THREADS), smem2, s, c);        \
+    } while (0)
+    if (D == 32) GO(1);
+    else if (D == 64) GO(2);
+    else if (D == 128) GO(4);
+    else GO(8);
+#undef GO
+    return launch_status();
+}
+
 // ------------------------------------------------------------------ finish
 // out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * weight[:] * sigmoid(gate[t, h, :]) * scale; a
 // warp per (token, head).

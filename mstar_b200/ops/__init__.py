@@ -1627,12 +1627,23 @@ def delta_prepare(proj: torch.Tensor, conv_w: torch.Tensor, a_proj: torch.Tensor
     return q, k, v, beta, decay
 
 
+DELTA_PIECE = 16            # tokens of a piece of the delta-rule scan
+DELTA_PIECES_FROM = 64      # entries of this many tokens or more are scanned in pieces
+DELTA_PIECES_DIMS = (32, 64, 128, 256)     # key sizes the scan in pieces takes
+
+
 def delta_scan(q, k, v, beta, decay, qo_indptr, slots, state: torch.Tensor, entries: int,
                heads: int, kv_heads: int, dim: int, vdim: int, taps: int,
                max_q_len: int = 1 << 30) -> torch.Tensor:
     """The gated delta rule over the tokens of ``entries`` batch entries, each continuing the
     matrix in its slot (updated in place).  ``max_q_len``: the longest entry (a bound will do;
-    short entries stage fewer tokens at a time).  Returns float [tokens, heads * vdim]."""
+    short entries stage fewer tokens at a time).  Returns float [tokens, heads * vdim].
+
+    A step with an entry of ``DELTA_PIECES_FROM`` tokens or more (and ``dim`` 32, 64, 128 or 256) is
+    scanned in pieces of 16 tokens: what does not depend on the state (decayed keys and
+    queries, the keys' products among themselves) is made for all pieces side by side, and
+    the chain from token to token shrinks to a scalar a token (MSTAR_DELTA_PIECES=0: never;
+    1: always)."""
     _need_cuda(q, k, v, beta, decay, qo_indptr, slots, state)
     for t in (q, k, v, beta, decay):
         assert t.dtype == torch.float32 and t.is_contiguous()
@@ -1640,6 +1651,26 @@ def delta_scan(q, k, v, beta, decay, qo_indptr, slots, state: torch.Tensor, entr
     tokens = q.shape[0]
     out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
     offset = (taps - 1) * (2 * kv_heads * dim + heads * vdim)
+    longest = int(min(max_q_len, tokens))
+    forced = os.environ.get("MSTAR_DELTA_PIECES")
+    pieces = (forced == "1" or (forced != "0" and longest >= DELTA_PIECES_FROM))
+    if (pieces and dim in DELTA_PIECES_DIMS and tokens > 0 and offset % 4 == 0
+            and state.stride(0) % 4 == 0):
+        max_pieces = -(-longest // DELTA_PIECE)
+        floats = (3 * tokens * heads * dim + entries * max_pieces * heads * dim
+                  + 2 * tokens * heads * DELTA_PIECE)
+        work = torch.empty(floats, dtype=torch.float32, device=q.device)
+        code = lib.get("gated_delta").mstar_delta_scan_pieces(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(),
+            qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0), offset,
+            out.data_ptr(), work.data_ptr(), tokens, entries, longest, heads, kv_heads, dim, vdim,
+            _stream())
+        if code == -1:
+            raise KernelError(f"delta-rule scan in pieces refuses heads={heads}, "
+                              f"kv_heads={kv_heads}, dim={dim}")
+        check(code, "delta_scan_pieces")
+        lib.add_launches(1)
+        return out
     code = lib.get("gated_delta").mstar_delta_scan(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), beta.data_ptr(), decay.data_ptr(),
         qo_indptr.data_ptr(), slots.data_ptr(), state.data_ptr(), state.stride(0), offset,

@@ -49,6 +49,8 @@ _SIGNATURES = {
         "mstar_delta_scan": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _i, _i, _i, _i,
                              _i, _i, _vp],
         "mstar_delta_finish": [_vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _f, _vp],
+        "mstar_delta_scan_pieces": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _ll, _ll, _vp, _vp, _i,
+                                    _i, _i, _i, _i, _i, _i, _vp],
     },
     "matrix_memory": {
         "mstar_matrix_memory_scan": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _ll, _vp, _i,

@@ -324,6 +324,41 @@ def test_gated_delta_rule_alone(dtype, heads, kv_heads, dim, vdim, taps):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,taps",
+                         [(4, 2, 24, 20, 3), (2, 1, 128, 40, 2), (2, 2, 200, 9, 1), (5, 1, 64, 64, 3),
+                          (2, 2, 32, 12, 3), (2, 1, 256, 20, 2), (3, 1, 64, 7, 4)])
+def test_delta_rule_long_portions_in_pieces(dtype, heads, kv_heads, dim, vdim, taps):
+    """A portion long enough to be scanned in pieces of 16 tokens (what does not depend on the
+    state made ahead for all pieces, a scalar chain within a piece; key sizes of 32, 64, 128
+    and 256 take that form, the others and a state that does not start on a 16-byte boundary
+    the token-by-token kernel), beside a short portion
+    of another request in the same batch; then more tokens of both, a portion that is no
+    multiple of 16 and a last one of a single token: against the token-by-token recurrence."""
+    from mstar_b200 import ops
+    from mstar_b200.parts import LayerCache
+
+    m = U.right(heads, kv_heads, dim, vdim, taps)
+    part, spec, p = delta_part(m, 96, dtype, seed=dim + 1)
+    T = ops.DELTA_PIECES_FROM + 3 * ops.DELTA_PIECE + 5
+    x = rnd(T + 80, 96, seed=6)
+    want = P.plain_gated_delta(x.double().numpy(), p, "", m, EPS, {})
+    short = P.plain_gated_delta(x[:9].double().numpy(), p, "", m, EPS, {})
+    size = ops.gated_delta_state_size(heads, kv_heads, dim, vdim, taps)
+    slots = torch.randn(3, size, device=DEV)
+    slots[:2].zero_()
+    cache = LayerCache(state=slots)
+    got = part.forward(dev(torch.cat([x[:5], x[:T]]), dtype), step_ctx([5, T], [0, 0], [1, 0]), cache)
+    close(got[5:], want[:T], dtype, "pieces", bf16=5e-2)
+    close(got[:5], short[:5], dtype, "short beside pieces", bf16=5e-2)
+    more = part.forward(dev(torch.cat([x[5:9], x[T:T + 79]]), dtype), step_ctx([4, 79], [5, T], [1, 0]),
+                        cache)
+    close(more[4:], want[T:T + 79], dtype, "after pieces", bf16=5e-2)
+    close(more[:4], short[5:], dtype, "short after pieces", bf16=5e-2)
+    last = part.forward(dev(x[T + 79:], dtype), step_ctx([1], [T + 79], [0]), cache)
+    close(last, want[T + 79:], dtype, "one more token", bf16=5e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_delta_rule_state_is_carried_a_long_way(dtype):
     """Decays close to one: what the first tokens wrote is still read hundreds of tokens on, so
     a state lost or reset at a portion's edge shows.  The plain model without its first
